@@ -1,7 +1,8 @@
 // Routing of a mixture of experts, and the norm that follows a sublayer.
 //
-// moe_topk: per token, from float router logits [T, E]: scores = softmax over all experts (score_fn 0) or
-//   sigmoid of each logit by itself (score_fn 1); experts form
+// moe_topk: per token, from float router logits [T, E] (plus a bias per expert, if given): scores = softmax over all
+//   experts (score_fn 0), sigmoid of each logit by itself (score_fn 1), or the logits themselves, ranked as they are,
+//   with the softmax over the chosen ones only as weights (score_fn 2); experts form
 //   `groups` equal groups of neighbours, a group's score is its largest, only experts of the best `keep`
 //   groups can be chosen (groups <= 1: no such limit); the `top` largest scores are chosen; their weights
 //   are the scores themselves, or the scores divided by their sum (`renorm`). All in float. Of equal
@@ -21,7 +22,8 @@ constexpr int MAX_E = 1024;      // experts a warp can rank (32 per lane)
 
 __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ logits, int T, int E, int groups,
                                                        int keep, int top, int renorm, int score_fn,
-                                                       int* __restrict__ idx, float* __restrict__ wt) {
+                                                       const float* __restrict__ bias, int* __restrict__ idx,
+                                                       float* __restrict__ wt) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float sm[];            // per warp: E scores, then E flags (1 allowed)
@@ -30,15 +32,18 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
   if (t >= T) return;
   float* s = sm + (size_t)warp * 2 * E;
   float* ok = s + E;
-  const float* z = logits + (size_t)t * E;
-  if (score_fn == 1) {
-    for (int e = lane; e < E; e += 32) { s[e] = 1.f / (1.f + expf(-z[e])); ok[e] = 1.f; }
+  const float* zr = logits + (size_t)t * E;
+  auto z = [&](int e) { return bias ? zr[e] + bias[e] : zr[e]; };
+  if (score_fn == 2) {
+    for (int e = lane; e < E; e += 32) { s[e] = z(e); ok[e] = 1.f; }
+  } else if (score_fn == 1) {
+    for (int e = lane; e < E; e += 32) { s[e] = 1.f / (1.f + expf(-z(e))); ok[e] = 1.f; }
   } else {
     float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z(e));
     m = warp_max(m);
     float sum = 0.f;
-    for (int e = lane; e < E; e += 32) { const float v = expf(z[e] - m); s[e] = v; sum += v; }
+    for (int e = lane; e < E; e += 32) { const float v = expf(z(e) - m); s[e] = v; sum += v; }
     sum = warp_sum(sum);
     const float inv = 1.f / sum;
     for (int e = lane; e < E; e += 32) { s[e] *= inv; ok[e] = 1.f; }
@@ -68,9 +73,9 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
       __syncwarp();
     }
   }
-  float chosen_sum = 0.f;
+  float chosen_sum = 0.f, first_best = 0.f;
   for (int r = 0; r < top; ++r) {
-    float best = -1.f; int be = 0x7fffffff;
+    float best = -INFINITY; int be = 0x7fffffff;
     for (int e = lane; e < E; e += 32)
       if (ok[e] == 1.f && s[e] > best) { best = s[e]; be = e; }
 #pragma unroll
@@ -80,11 +85,14 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
       if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
     }
     __syncwarp();
-    if (lane == 0) { ok[be] = 2.f; idx[(size_t)t * top + r] = be; wt[(size_t)t * top + r] = best; }
-    chosen_sum += best;
+    if (r == 0) first_best = best;
+    // ranked logits: the weight is exp(logit - largest chosen logit), divided by the sum of these below
+    const float val = score_fn == 2 ? expf(best - first_best) : best;
+    if (lane == 0) { ok[be] = 2.f; idx[(size_t)t * top + r] = be; wt[(size_t)t * top + r] = val; }
+    chosen_sum += val;
     __syncwarp();
   }
-  if (renorm && lane < top) wt[(size_t)t * top + lane] /= chosen_sum;
+  if ((renorm || score_fn == 2) && lane < top) wt[(size_t)t * top + lane] /= chosen_sum;
 }
 
 // counts -> segments -> tiles -> places. n = T * top pairs, pair i = token i / top, slot i % top.
@@ -150,13 +158,14 @@ __global__ void add_row_kernel(float* __restrict__ h, const float* __restrict__ 
 }  // namespace
 
 RLLM_API int rllm_moe_topk(const float* logits, int T, int E, int groups, int keep, int top, int renorm, int score_fn,
-                           int* idx, float* wt, void* stream) {
+                           const float* bias, int* idx, float* wt, void* stream) {
   if (T <= 0) return 0;
-  if (E <= 0 || E > MAX_E || top <= 0 || top > 32 || top > E || score_fn < 0 || score_fn > 1) return ERR_BAD_SIZE;
+  if (E <= 0 || E > MAX_E || top <= 0 || top > 32 || top > E || score_fn < 0 || score_fn > 2) return ERR_BAD_SIZE;
+  if (score_fn == 2 && groups > 1) return ERR_BAD_SIZE;      // a group's score is a maximum of non-negative scores
   if (groups > 1 && (E % groups || keep <= 0 || keep > groups || top > (E / groups) * keep)) return ERR_BAD_SIZE;
   const size_t smem = (size_t)4 * 2 * E * sizeof(float);
   return launch_ex(moe_topk_kernel, dim3((T + 3) / 4), dim3(128), smem, (cudaStream_t)stream, 1, logits, T, E, groups,
-                   keep, top, renorm, score_fn, idx, wt);
+                   keep, top, renorm, score_fn, bias, idx, wt);
 }
 
 // tiles: room for n / tile_rows + E entries of 3 ints.

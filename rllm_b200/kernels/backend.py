@@ -206,9 +206,9 @@ class Backend:
         down = self._mix.tile_rows(x.dtype, w_down.shape[2], w_down.shape[2], n_rows)
         return up if up == down else 64         # one of them stays on the CUDA cores: both take its tiles
 
-    def route(self, logits, top, groups=1, keep=1, renorm=False, tile_rows=64, score="softmax"):
-        """Router logits -> the plan of the experts' grouped products (all on the device)."""
-        idx, wt = self._mix.moe_topk(logits, top, groups, keep, renorm, score)
+    def route(self, logits, top, groups=1, keep=1, renorm=False, tile_rows=64, score="softmax", bias=None):
+        """Router logits (plus a float bias per expert) -> the plan of the experts' grouped products (all on the device)."""
+        idx, wt = self._mix.moe_topk(logits, top, groups, keep, renorm, score, bias)
         return idx, wt, self._mix.moe_plan(idx, wt, logits.shape[1], tile_rows)
 
     def _tc_experts(self, a, w, plan):
@@ -358,6 +358,86 @@ class Backend:
 
     def gla_finish(self, *a, **k):
         return self._mix.gla_finish(*a, **k)
+
+    # ---- recurrent mixers with a short convolution, attention with mixed heads, layers whose sublayers run side by
+    # side (library "hybrid")
+    @property
+    def _hy(self):
+        from . import hybrid
+        return hybrid
+
+    def pair_embed(self, ctx, table, pair, buckets, mul_prev, mul_cur, norm_w, eps, prev_state):
+        """The embedded rows plus the rows of a table addressed by a hash of each token and the one before it, normed."""
+        return self._hy.pair_embed(ctx.token_ids, ctx.positions, ctx.token_seq, ctx.cu_q, ctx.num_seqs,
+                                   ctx.state_slots if prev_state is not None else None, prev_state, table, pair, buckets,
+                                   mul_prev, mul_cur, norm_w, eps, err=ctx.extras.get("err_flag"))
+
+    def combine(self, h, *outputs):
+        """h += the sublayers' outputs, in float and in one pass. An output is a float tensor [T, H] / [T, parts, H],
+        `Summands` (parts and an ungated second summand) or `NormedSum` (summands that are RMS-normed first)."""
+        normed, plain, coef, eps = [], [], 1.0, 1e-6
+        for y in outputs:
+            if y is None:
+                continue
+            if hasattr(y, "terms"):
+                if normed:
+                    raise ops.KernelError("combine takes the normed summands of one sublayer")
+                normed, coef, eps = list(y.terms), y.coef, y.eps
+            elif hasattr(y, "parts"):
+                if y.extra_gate is not None:
+                    raise ops.KernelError("combine takes no gated summand")
+                plain += [t for t in (y.parts, y.extra) if t is not None]
+            else:
+                plain.append(y)
+        return self._hy.combine(h, normed, coef, eps, plain)
+
+    def linear_glu(self, x, w_gate_up, act, limit=0.0, alpha=1.0):
+        """act(x Wg^T, x Wu^T) with w_gate_up = [Wg; Wu] in the run dtype; the two products stay float until the
+        activation has run."""
+        if act == "silu":
+            return self.linear_swiglu(x, w_gate_up)
+        return self._hy.glu_act(self.linear_f32(x, w_gate_up, tag="gate_up"), self.dtype, act, limit, alpha)
+
+    def experts_glu_up(self, x, w_gate_up, plan, act, limit=0.0, alpha=1.0):
+        """act(g, u) for every sorted row of the plan, g and u the row's token times the gate and the up rows of the
+        row's expert. W [E, 2F, K]: an expert's gate rows, then its up rows."""
+        gu = torch.empty((plan.n_rows, w_gate_up.shape[1]), dtype=torch.float32, device=x.device)
+        if self._tc_experts(x, w_gate_up, plan):
+            rows = self._mix.gather_rows_bf16(x, plan.rows_tok)
+            self._mix.grouped_gemm_tc(rows, w_gate_up, plan, gu, self._mix.GEPI_STORE_F32,
+                                      err=self._sm100.init(self.device).err)
+        else:
+            self._mix.grouped_gemm_ragged(x, w_gate_up, plan, gu, self._mix.GEPI_STORE_F32, gather=True)
+        return self._hy.glu_act(gu, x.dtype, act, limit, alpha)
+
+    def add_bias_f32(self, y, bias):
+        return self._hy.add_bias_f32(y, bias)
+
+    def short_conv(self, x, col0, channels, w, bias, ctx, tail, silu=True):
+        return self._hy.short_conv(x, col0, channels, w, bias, ctx.token_seq, ctx.positions, ctx.cu_q, ctx.num_seqs,
+                                   ctx.state_slots, tail, silu)
+
+    def unit_heads(self, *a, **k):
+        return self._hy.unit_heads(*a, **k)
+
+    def softplus_decay(self, *a, **k):
+        return self._hy.softplus_decay(*a, **k)
+
+    def state_scan(self, q, q_heads, k, k_heads, v, decay, heads, dim, vdim, ctx, state, beta=None, vscale=None, skip=None):
+        return self._hy.state_scan(q, q_heads, k, k_heads, v, decay, heads, dim, vdim, ctx.cu_q, ctx.num_seqs,
+                                   ctx.state_slots, state, beta, vscale, skip)
+
+    def gated_norm(self, y, gate, gate_col0, weight, eps, groups, gate_first, act):
+        return self._hy.gated_norm(y, gate, gate_col0, weight, eps, groups, self.dtype, gate_first, act)
+
+    def value_norm_store(self, proj, k_off, v_off, nkv, kd, vd, eps, norm, cache):
+        if cache.writes:
+            self._hy.value_norm_store(proj, k_off, v_off, nkv, kd, vd, eps, norm, cache.slots, cache.k, cache.v)
+
+    def talk_attention(self, q, cache, ctx, nh, scale, mix, window, chunk, sinks):
+        """Attention whose heads' softmax weights are mixed by `mix` before they meet the values."""
+        return self._hy.talk_attention_simt(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, nh, scale,
+                                            mix, window, chunk, sinks)
 
     # ---- selection
     def argmax(self, logits):

@@ -26,7 +26,7 @@ ops.register_signatures("experts", {
     "rllm_grouped_gemm_tc_supported": [_LL, c_int, c_int],
     "rllm_grouped_gemm_tc": [c_int, _P, _LL, _LL, _P, c_int, c_int, c_int, _P, _LL, _P, _P, c_int, _P, _P, _P, _P],
     "rllm_gather_rows_bf16": [_P, _LL, _P, _P, c_int, c_int, _P],
-    "rllm_moe_topk": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
+    "rllm_moe_topk": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "rllm_moe_plan": [_P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
     "rllm_rmsnorm_add": [_P, c_int, _P, _P, c_int, c_int, c_float, _P],
     "rllm_add_row": [_P, _P, c_int, c_int, _P],
@@ -126,13 +126,17 @@ def tile_rows(dtype: torch.dtype, lda: int, K: int, n_rows: int = 1 << 30) -> in
     return _fn("experts", "rllm_grouped_gemm_tile_rows")(ops._DT[dtype], int(lda), int(K), int(min(n_rows, 1 << 30)))
 
 
-SCORE_FNS = {"softmax": 0, "sigmoid": 1}
+SCORE_FNS = {"softmax": 0, "sigmoid": 1, "softmax_chosen": 2}
 
 
 def moe_topk(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1,
-             renorm: bool = False, score: str = "softmax") -> tuple[torch.Tensor, torch.Tensor]:
+             renorm: bool = False, score: str = "softmax", bias: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """(chosen experts int32 [T, top], their weights float32 [T, top]) from float32 router logits [T, E];
-    `score`: "softmax" over all experts, or "sigmoid" of each logit by itself."""
+    `score`: "softmax" over all experts, "sigmoid" of each logit by itself, or "softmax_chosen": the logits are
+    ranked as they are and the weights are the softmax over the chosen ones only. `bias` float32 [E] is added to
+    the logits first."""
+    if bias is not None:
+        _f32(bias, "router bias", (logits.shape[1],))
     if score not in SCORE_FNS:
         raise KernelError(f"router score {score!r} has no kernel (known: {sorted(SCORE_FNS)})")
     _f32(logits, "router logits")
@@ -140,7 +144,7 @@ def moe_topk(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1,
     idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     wt = torch.empty((T, top), dtype=torch.float32, device=logits.device)
     _check(_fn("experts", "rllm_moe_topk")(logits.data_ptr(), T, E, int(groups), int(keep), int(top), int(bool(renorm)),
-                                           SCORE_FNS[score], idx.data_ptr(), wt.data_ptr(), _stream()), "moe_topk")
+                                           SCORE_FNS[score], ops._ptr(bias), idx.data_ptr(), wt.data_ptr(), _stream()), "moe_topk")
     return idx, wt
 
 

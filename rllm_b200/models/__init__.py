@@ -2,5 +2,6 @@ from .model import LayerCall, Model
 from . import llama  # registers LlamaForCausalLM
 from . import zukotar  # registers Zukotar
 from . import livovik  # registers Livovik
+from . import bazulorn  # registers Bazulorn
 
-__all__ = ["LayerCall", "Model", "llama", "zukotar", "livovik"]
+__all__ = ["LayerCall", "Model", "llama", "zukotar", "livovik", "bazulorn"]

@@ -144,3 +144,70 @@ class SinkGQAttention(Part):
 
 
 register_part("mixer", "gqa_sink", SinkGQAttention)
+
+
+class TalkingHeadsAttention(Part):
+    """Grouped-query attention whose heads' softmax weights are mixed by a matrix before they meet the values:
+
+        p_g(i, j) = exp(s_g(i, j)) / (exp(sink) + sum_j' exp(s_g(i, j')))       s_g = scale * q_g . k_c(g)
+        w_h(i, j) = sum_g M[h, g] p_g(i, j)            o_h(i) = sum_j w_h(i, j) v_c(h)(j)
+
+    with c(h) the key/value head of query head h and M the tensor `talk` [heads, heads]. Every piece is a constructor
+    argument: keys of `head_dim` and values of `v_dim` numbers per head; `bias`: the q, k and v projections have
+    biases (`<name>.b`); `value_norm`: each value head is divided by its root mean square (no weight) and cached so;
+    the mask is causal with an optional `window` and/or `chunk`; `sink`: a fixed score whose exponential joins every
+    head's denominator (None: the plain softmax). Positions do not enter the scores. Scores, softmax, the mix and the
+    value norm are float. `forward(..., residual=None)` returns the float output."""
+    graph_safe = True
+    returns_output = True
+
+    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, v_dim: int | None = None,
+                 scale: float | None = None, window: int | None = None, chunk: int | None = None, bias: bool = False,
+                 value_norm: bool = False, sink: float | None = None, eps: float = 1e-6,
+                 names=("q", "k", "v", "o", "talk")):
+        if heads % kv_heads:
+            raise ValueError(f"heads {heads} must be a multiple of kv_heads {kv_heads}")
+        v_dim = head_dim if v_dim is None else v_dim
+        if not 0 < v_dim <= 256 or head_dim <= 0:
+            raise ValueError(f"head sizes {head_dim} / {v_dim}: values must lie in 1..256")
+        self.hidden, self.heads, self.kv_heads, self.head_dim, self.v_dim = hidden, heads, kv_heads, head_dim, v_dim
+        self.scale = head_dim ** -0.5 if scale is None else float(scale)
+        self.window, self.chunk, self.bias, self.value_norm = window, chunk, bias, value_norm
+        self.sink, self.eps, self.names = sink, float(eps), names
+        self.w_qkv = self.b_qkv = self.w_o = self.talk = None
+
+    def params(self):
+        W, H, G, D, V = self.hidden, self.heads, self.kv_heads, self.head_dim, self.v_dim
+        q, k, v, o, talk = self.names
+        ps = [Param("w_qkv", (Source(q, (H * D, W)), Source(k, (G * D, W)), Source(v, (G * V, W)))),
+              Param("w_o", (Source(o, (W, H * V)),)),
+              Param("talk", (Source(talk, (H, H)),), role="vector")]
+        if self.bias:
+            ps.append(Param("b_qkv", (Source(q + ".b", (H * D,)), Source(k + ".b", (G * D,)), Source(v + ".b", (G * V,)))))
+        return ps
+
+    def cache_spec(self):
+        return KVCacheSpec(self.kv_heads, self.head_dim, self.window, self.chunk,
+                           None if self.v_dim == self.head_dim else self.v_dim)
+
+    def finalize(self, device, dtype):
+        import torch
+        self._talk = self.talk.float().contiguous()
+        self._sinks = None if self.sink is None else torch.full((self.heads,), float(self.sink), dtype=torch.float32,
+                                                                device=device)
+
+    def forward(self, x, ctx, cache, residual=None):
+        be = ctx.backend
+        x = x.tensor() if hasattr(x, "tensor") else x
+        H, G, D, V = self.heads, self.kv_heads, self.head_dim, self.v_dim
+        proj = be.linear(x, self.w_qkv, bias=self.b_qkv, tag="qkv")                      # [T, q | k | v]
+        be.value_norm_store(proj, H * D, (H + G) * D, G, D, V, self.eps, self.value_norm, cache)
+        att = be.talk_attention(proj[:, : H * D], cache, ctx, H, self.scale, self._talk, self.window, self.chunk,
+                                self._sinks)
+        if residual is None:
+            return be.linear_f32(att, self.w_o, tag="o")
+        be.linear_residual(att, self.w_o, residual)
+        return None
+
+
+register_part("mixer", "gqa_talk", TalkingHeadsAttention)

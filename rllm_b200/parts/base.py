@@ -192,6 +192,15 @@ class Summands:
 
 
 @dataclass
+class NormedSum:
+    """A sublayer's output as coef * sum_i w_i * a_i / rms(a_i): `terms` pairs of float [T, hidden] and float
+    [hidden], for a block whose sum kernel norms them itself."""
+    terms: tuple
+    coef: float = 1.0
+    eps: float = 1e-6
+
+
+@dataclass
 class LayerCache:
     """What a mixer gets for its cache layer in one step.
 

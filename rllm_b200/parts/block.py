@@ -3,7 +3,8 @@ order (src/model/registry/llama.rs:163-245): h += mixer(norm(h)); h += ffn(norm(
 `SandwichBlock` norms each sublayer's output as well: h += norm_b(mixer(norm(h))), the same for
 the feed-forward, which may be absent. `LoopStep` is a block that only adds a learned vector to
 every row: what a pass of a looped stretch of layers begins with. `PostNormBlock` norms after the sum,
-h = norm(alpha h + sublayer(h)), the sublayers reading the stream itself."""
+h = norm(alpha h + sublayer(h)), the sublayers reading the stream itself. `ParallelBlock` has one norm whose
+output both sublayers read: h += mixer(n) + ffn(n), n = norm(h)."""
 from __future__ import annotations
 
 from .base import Param, Part, Source, register_part
@@ -149,6 +150,45 @@ class PostNormBlock(Part):
         return h
 
 
+class ParallelBlock(Part):
+    """h <- h + (mixer(n) + ffn(n)) with n = norm(h): one norm, both sublayers read its output, the feed-forward may
+    be absent. Sublayers return their float outputs (a tensor, `Summands`, or `NormedSum` for a mixer whose members are
+    normed before they are added); the sum of all of them and the residual sum are one float kernel. A mixer made
+    of several mixers gets a tuple of cache layers. `names`: checkpoint sub-prefixes of mixer and feed-forward; the
+    norm's weight is a tensor named by its `weight_name` under the block's prefix."""
+    graph_safe = True
+
+    def __init__(self, norm: Part, mixer: Part, ffn: Part | None = None, names=("mix.", "mlp.")):
+        self.norm, self.mixer, self.ffn, self.names = norm, mixer, ffn, names
+
+    def children(self):
+        return [p for p in (self.norm, self.mixer, self.ffn) if p is not None]
+
+    def set_prefix(self, prefix: str):
+        self.prefix = prefix
+        self.norm.prefix = prefix
+        for part, sub in ((self.mixer, self.names[0]), (self.ffn, self.names[1])):
+            if part is None:
+                continue
+            if hasattr(part, "set_prefix"):
+                part.set_prefix(prefix + sub)
+                continue
+            part.prefix = prefix + sub
+            for c in part.children():
+                if not c.prefix:
+                    c.prefix = part.prefix
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, h, ctx, cache):
+        """h: float32 residual stream [T, hidden], updated in place."""
+        n = self.norm.forward(h, ctx)
+        m = self.mixer.forward(n, ctx, cache, None)
+        f = None if self.ffn is None else self.ffn.forward(n, ctx, None)
+        return ctx.backend.combine(h, m, f)
+
+
 class LoopStep(Part):
     """h += table[index] on every row. The passes of one loop share the table [times, hidden]: the
     first owns the tensor (`owner` None), the others name the first."""
@@ -177,4 +217,5 @@ class LoopStep(Part):
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "sandwich", SandwichBlock)
 register_part("block", "postnorm", PostNormBlock)
+register_part("block", "parallel", ParallelBlock)
 register_part("block", "loop_step", LoopStep)

@@ -5,7 +5,7 @@ times `scale` for designs that scale it (1 otherwise; a head tied to the table u
 float32 and are computed only for the rows that were asked for."""
 from __future__ import annotations
 
-from .base import Param, Part, Source, register_part
+from .base import Param, Part, Source, StateSpec, register_part
 
 
 class Embedding(Part):
@@ -55,3 +55,42 @@ class OutputHead(Part):
 
 register_part("embedding", "table", Embedding)
 register_part("head", "linear", OutputHead)
+
+
+class PairEmbedding(Part):
+    """Token embedding plus a row of a second table addressed by a hash of the token and the one before it in its
+    sequence, (previous * mul_prev + token * mul_cur) mod buckets; a sequence's first token takes row `buckets` (the
+    table has buckets + 1 rows). The sum is RMS-normed with a weight (`norm_name`; None: no norm) and returned as the
+    float stream. The token before a portion's first one is per-request state (`StateSpec`, one int32), so a prompt
+    may be cut anywhere. `pair_name` None: the plain table, normed."""
+    graph_safe = True
+
+    def __init__(self, vocab: int, hidden: int, buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0, eps: float = 1e-6,
+                 name: str = "embed", pair_name: str | None = "bigram", norm_name: str | None = "embed.norm"):
+        self.vocab, self.hidden, self.buckets, self.mul_prev, self.mul_cur = vocab, hidden, buckets, mul_prev, mul_cur
+        self.eps, self.name, self.pair_name, self.norm_name = float(eps), name, pair_name, norm_name
+        if pair_name is not None and buckets <= 0:
+            raise ValueError("a pair table needs a positive number of buckets")
+        self.table = self.pair = self.norm_w = None
+
+    def params(self):
+        ps = [Param("table", (Source(self.name, (self.vocab, self.hidden)),))]
+        if self.pair_name is not None:
+            ps.append(Param("pair", (Source(self.pair_name, (self.buckets + 1, self.hidden)),)))
+        if self.norm_name is not None:
+            ps.append(Param("norm_w", (Source(self.norm_name, (self.hidden,), init="norm"),), role="vector"))
+        return ps
+
+    def cache_spec(self):
+        import torch
+        return None if self.pair_name is None else StateSpec((("prev", (), torch.int32),))
+
+    def finalize(self, device, dtype):
+        self._norm = None if self.norm_w is None else self.norm_w.float().contiguous()
+
+    def forward(self, ctx, cache=None):
+        return ctx.backend.pair_embed(ctx, self.table, self.pair, self.buckets, self.mul_prev, self.mul_cur, self._norm,
+                                      self.eps, None if cache is None else cache.state["prev"])
+
+
+register_part("embedding", "pair", PairEmbedding)

@@ -58,3 +58,36 @@ class ActFFN(Part):
 
 register_part("ffn", "swiglu", SwiGLU)
 register_part("ffn", "act", ActFFN)
+
+
+class GluFFN(Part):
+    """down(act(gate x, up x)), no biases, with the gated activation a constructor argument:
+    "silu": silu(g) u; "gelu_tanh": gelu(g) u in its tanh form; "swish_clamped": with g' = min(g, limit) and
+    u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1). Gate and up weights are stacked so that one product
+    yields both; the two halves stay float until the activation has run."""
+    graph_safe = True
+    returns_output = True
+    ACTS = ("silu", "gelu_tanh", "swish_clamped")
+
+    def __init__(self, hidden: int, intermediate: int, act: str = "silu", limit: float = 0.0, alpha: float = 1.0,
+                 names=("gate", "up", "down")):
+        if act not in self.ACTS:
+            raise ValueError(f"activation {act!r} is not known (known: {self.ACTS})")
+        self.hidden, self.intermediate, self.act, self.limit, self.alpha = hidden, intermediate, act, float(limit), float(alpha)
+        self.names = names
+        self.w_gate_up = self.w_down = None
+
+    def params(self):
+        H, I = self.hidden, self.intermediate
+        g, u, d = self.names
+        return [Param("w_gate_up", (Source(g, (I, H)), Source(u, (I, H)))), Param("w_down", (Source(d, (H, I)),))]
+
+    def forward(self, x, ctx, residual):
+        be = ctx.backend
+        a = be.linear_glu(x, self.w_gate_up, self.act, self.limit, self.alpha)
+        if residual is None:
+            return be.linear_f32(a, self.w_down, tag="down")
+        be.linear_residual(a, self.w_down, residual)
+
+
+register_part("ffn", "glu", GluFFN)

@@ -114,3 +114,61 @@ class GatedRoutedExperts(Part):
 
 register_part("ffn", "moe", RoutedExperts)
 register_part("ffn", "moe_gated", GatedRoutedExperts)
+
+
+class GluRoutedExperts(Part):
+    """A mixture of gated experts whose weights multiply the experts' *outputs*: expert(h) = W_down act(W_gate h,
+    W_up h) without biases, act one of `GluFFN.ACTS` with its `limit` and `alpha`. Router logits z = W_router h
+    (+ a bias per expert, tensor `router.b`) in float; `score` "softmax_chosen": the `top` largest logits are chosen
+    and their weights are the softmax over the chosen logits only ("softmax" and "sigmoid" as for the other routed
+    feed-forwards). `shared`: a dense feed-forward every token uses (its tensors under `shared.`), added as it is.
+    Returns `Summands`: one float row per (token, chosen expert) and the shared expert's output; the block adds them."""
+    graph_safe = True
+    returns_output = True
+
+    def __init__(self, hidden: int, ff: int, experts: int, top: int, act: str = "silu", limit: float = 0.0,
+                 alpha: float = 1.0, score: str = "softmax_chosen", renorm: bool = False, router_bias: bool = False,
+                 shared: Part | None = None):
+        if top > experts:
+            raise ValueError(f"top {top} exceeds the {experts} experts")
+        self.hidden, self.ff, self.experts, self.top = hidden, ff, experts, top
+        self.act, self.limit, self.alpha = act, float(limit), float(alpha)
+        self.score, self.renorm, self.router_bias, self.shared = score, renorm, router_bias, shared
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+
+    def children(self):
+        return [] if self.shared is None else [self.shared]
+
+    def set_prefix(self, prefix: str):
+        self.prefix = prefix
+        if self.shared is not None:
+            self.shared.prefix = prefix + "shared."
+
+    def params(self):
+        E, W, F = self.experts, self.hidden, self.ff
+        ps = [Param("w_router", (Source("router", (E, W)),)),
+              Param("w_gate_up", tuple(Source(f"e{e}.{n}", (F, W)) for e in range(E) for n in ("gate", "up"))),
+              Param("w_down", tuple(Source(f"e{e}.down", (W, F)) for e in range(E)))]
+        if self.router_bias:
+            ps.append(Param("b_router", (Source("router.b", (E,)),), role="vector"))
+        return ps
+
+    def finalize(self, device, dtype):
+        self._gate_up = self.w_gate_up.view(self.experts, 2 * self.ff, self.hidden)
+        self._down = self.w_down.view(self.experts, self.hidden, self.ff)
+        self._bias = None if self.b_router is None else self.b_router.float().contiguous()
+
+    def forward(self, x, ctx, residual=None):
+        if residual is not None:
+            raise NotImplementedError("GluRoutedExperts returns its summands; the block adds them")
+        be = ctx.backend
+        x = x.tensor() if hasattr(x, "tensor") else x
+        T = x.shape[0]
+        _, _, plan = be.route(be.linear_f32(x, self.w_router, tag="router"), self.top, renorm=self.renorm, score=self.score,
+                              bias=self._bias, tile_rows=be.expert_tile_rows(x, self._gate_up, self._down, T * self.top))
+        act = be.experts_glu_up(x, self._gate_up, plan, self.act, self.limit, self.alpha)
+        parts = be.experts_down(act, self._down, plan, T, self.top, scale=True)
+        return Summands(parts, None if self.shared is None else self.shared.forward(x, ctx, None))
+
+
+register_part("ffn", "moe_glu", GluRoutedExperts)
