@@ -162,10 +162,35 @@ def _livovik_sizes():
     return out
 
 
+def _bazulorn_sizes():
+    """Four layers as in the Zukotar sizes beside them (attention, recurrent, recurrent, attention; routed
+    feed-forwards with equal experts, top and inner size, here with the clamped gate and a shared expert of one
+    expert's size). The attention layers have 128-wide heads over four key/value heads and a window longer than every
+    context here, beside a state-space recurrence of the model's width in heads of 64 channels and 128 state rows; the
+    delta-rule layers have as many heads of 128 x 128 as Zukotar's gated linear attention."""
+    out = {}
+    for name, W, H, E, top, ff in (("w2048", 2048, 16, 16, 6, 2048), ("w4096", 4096, 32, 32, 8, 2688)):
+        moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": E, "top": top},
+               "shared": {"ff": ff, "limit": 7.0}}
+        par = {"type": "parallel", "mlp": moe, "mixer": {
+            "left": {"heads": H, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 4096}},
+            "right": {"heads": W // 64, "vdim": 64, "state": 128, "groups": 4, "norm_groups": 4, "conv": 4}}}
+        rec = {"type": "channel_delta", "mlp": moe,
+               "mixer": {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 16, "gate_rank": 64}}
+        out[name] = {"architecture": "Bazulorn", "vocab": 32000, "width": W, "norm": {"eps": 1e-6},
+                     "embedding": {"bigram": {"buckets": 65521, "mul_prev": 911, "mul_cur": 31}},
+                     "layers": [par, rec, rec, par]}
+    return out
+
+
 def design_sizes(design):
-    """name -> (the design's configuration, Llama layers of equal width, depth and active feed-forward weights)."""
+    """name -> (the design's configuration, the layers beside it: Llama layers of equal width, depth and active
+    feed-forward weights, or for Bazulorn the Zukotar model of equal width, depth, heads and experts)."""
     if design == "livovik":
         return _livovik_sizes()
+    if design == "bazulorn":
+        zk = design_sizes("zukotar")
+        return {name: (cfg, zk[name][0]) for name, cfg in _bazulorn_sizes().items()}
     assert design == "zukotar"
     out = {}
     # width, heads, latent rank, experts, top, expert ff, groups, keep | llama heads, kv heads, head size, intermediate
@@ -209,7 +234,7 @@ def compare_designs(design, W, K):
 
     for name, cfgs in design_sizes(design).items():
         res[name] = {}
-        for arch, cfg in zip((design, "llama"), cfgs):
+        for arch, cfg in zip((design, "zukotar" if design == "bazulorn" else "llama"), cfgs):
             vocab = cfg.get("vocab", cfg.get("vocab_size"))
             prompt = [(7 * i + 3) % vocab for i in range(T)]
             r = {}
@@ -264,9 +289,10 @@ def main():
     ap.add_argument("--workloads", default="", help="comma-separated: mixed_3b, continuous_8b, or all")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (for profiling; the JSON line then lacks the other parts)")
-    ap.add_argument("--designs", default="", choices=["", "zukotar", "livovik"],
+    ap.add_argument("--designs", default="", choices=["", "zukotar", "livovik", "bazulorn"],
                     help="instead of the default workload: prefill and decode of this design beside Llama layers of "
-                         "equal size (random weights), with the time per operation; prints its own JSON line")
+                         "equal size (bazulorn: beside Zukotar layers), random weights, with the time per operation; "
+                         "prints its own JSON line")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket one timed step with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     a = ap.parse_args()
