@@ -249,6 +249,131 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const TG* __restr
 
 inline unsigned blocks_for(long long n) { return (unsigned)((n + 255) / 256 > 65535 * 8 ? 65535 * 8 : (n + 255) / 256); }
 
+// The same recurrence for heads of 32 * SPLIT key channels (32, 64, 128, 256), the sizes known when compiled: a thread's
+// 32 channels are neighbours (sub * 32 ...), so queries, keys and decays come from shared memory in pieces of four
+// (rows padded by four floats a lane share, which keeps the shares on different banks), and the sums over channels
+// run as four chains side by side. Same ownership, same staging and, per position, the same order of sums
+// whatever the cut into steps.
+template <typename TB, int SPLIT, bool PERCH>
+__global__ void __launch_bounds__(128) state_scan_fast_kernel(ScanArgs a) {
+  pdl_launch();
+  pdl_wait();
+  constexpr int R = 32, DIM = R * SPLIT, LDK = SPLIT * (R + 4), COLS = 128 / SPLIT;
+  extern __shared__ __align__(16) float sm[];
+  const int vdim = a.vdim, ch = a.ch, H = a.H;
+  float* qs = sm;                                    // [ch][LDK]
+  float* ks = qs + ch * LDK;
+  float* as = ks + ch * LDK;                         // [ch][LDK] or [ch]
+  float* vs = as + (PERCH ? ch * LDK : ch);          // [ch][COLS]
+  float* bs = vs + ch * COLS;                        // [ch] beta, [ch] vscale
+  const int seq = blockIdx.x, h = blockIdx.y;
+  const int sub = threadIdx.x % SPLIT, col = threadIdx.x / SPLIT;
+  const int v = blockIdx.z * COLS + col;
+  const bool vok = v < vdim;
+  const int row0 = a.cu_q[seq], row1 = a.cu_q[seq + 1];
+  const int slot = a.state_slots ? a.state_slots[seq] : -1;
+  const int qh = h / (H / a.q_heads), kh = h / (H / a.k_heads);
+  float S[R];
+  float* sp = a.state + (((long long)(slot < 0 ? 0 : slot) * H + h) * DIM + sub * R) * vdim + v;
+#pragma unroll
+  for (int i = 0; i < R; ++i) S[i] = (slot >= 0 && vok) ? sp[(long long)i * vdim] : 0.f;
+  const float skip = a.skip ? a.skip[h] : 0.f;
+  const bool delta = a.beta != nullptr;
+  for (int c0 = row0; c0 < row1; c0 += ch) {
+    const int n = min(ch, row1 - c0);
+    __syncthreads();
+    for (int x = threadIdx.x; x < n * DIM; x += 128) {
+      const int cc = x / DIM, k = x % DIM;
+      const long long r = c0 + cc;
+      const int at = cc * LDK + (k / R) * (R + 4) + k % R;
+      qs[at] = a.q[r * a.q_ld + qh * DIM + k];
+      ks[at] = a.k[r * a.k_ld + kh * DIM + k];
+      if (PERCH) as[at] = a.decay[(r * H + h) * DIM + k];
+    }
+    for (int x = threadIdx.x; x < n * COLS; x += 128) {
+      const int cc = x / COLS, c = x % COLS;
+      const int vv = blockIdx.z * COLS + c;
+      vs[x] = vv < vdim ? a.v[(long long)(c0 + cc) * a.v_ld + h * vdim + vv] : 0.f;
+    }
+    for (int cc = threadIdx.x; cc < n; cc += 128) {
+      const long long r = c0 + cc;
+      if (!PERCH) as[cc] = a.decay[r * H + h];
+      bs[cc] = delta ? sigmoid_f(to_f32(reinterpret_cast<const TB*>(a.beta)[r * a.beta_ld + h])) : 1.f;
+      bs[ch + cc] = a.vscale ? a.vscale[r * H + h] : 1.f;
+    }
+    __syncthreads();
+    for (int cc = 0; cc < n; ++cc) {
+      const float4* kr = reinterpret_cast<const float4*>(ks + cc * LDK + sub * (R + 4));
+      const float4* qr = reinterpret_cast<const float4*>(qs + cc * LDK + sub * (R + 4));
+      const float x = vs[cc * COLS + col];
+      float kk[R];
+#pragma unroll
+      for (int i = 0; i < R / 4; ++i) {
+        const float4 t = kr[i];
+        kk[4 * i] = t.x; kk[4 * i + 1] = t.y; kk[4 * i + 2] = t.z; kk[4 * i + 3] = t.w;
+      }
+      if (PERCH) {
+        const float4* ar = reinterpret_cast<const float4*>(as + cc * LDK + sub * (R + 4));
+#pragma unroll
+        for (int i = 0; i < R / 4; ++i) {
+          const float4 t = ar[i];
+          S[4 * i] *= t.x; S[4 * i + 1] *= t.y; S[4 * i + 2] *= t.z; S[4 * i + 3] *= t.w;
+        }
+      } else {
+        const float al = as[cc];
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[i] *= al;
+      }
+      float u;
+      if (delta) {
+        float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+          r0 = fmaf(S[i], kk[i], r0); r1 = fmaf(S[i + 1], kk[i + 1], r1);
+          r2 = fmaf(S[i + 2], kk[i + 2], r2); r3 = fmaf(S[i + 3], kk[i + 3], r3);
+        }
+        float r = (r0 + r1) + (r2 + r3);
+#pragma unroll
+        for (int o = 1; o < SPLIT; o <<= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+        u = bs[cc] * (x - r);
+      } else {
+        u = bs[ch + cc] * x;
+      }
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < R / 4; ++i) {
+        const float4 t = qr[i];
+        S[4 * i] = fmaf(kk[4 * i], u, S[4 * i]); o0 = fmaf(S[4 * i], t.x, o0);
+        S[4 * i + 1] = fmaf(kk[4 * i + 1], u, S[4 * i + 1]); o1 = fmaf(S[4 * i + 1], t.y, o1);
+        S[4 * i + 2] = fmaf(kk[4 * i + 2], u, S[4 * i + 2]); o2 = fmaf(S[4 * i + 2], t.z, o2);
+        S[4 * i + 3] = fmaf(kk[4 * i + 3], u, S[4 * i + 3]); o3 = fmaf(S[4 * i + 3], t.w, o3);
+      }
+      float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+      for (int w = 1; w < SPLIT; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+      if (sub == 0 && vok) a.out[((long long)(c0 + cc) * H + h) * vdim + v] = fmaf(skip, x, o);
+    }
+  }
+  if (slot >= 0 && vok) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) sp[(long long)i * vdim] = S[i];
+  }
+}
+
+template <typename TB>
+int launch_scan_fast(const ScanArgs& a, int split, bool perch, dim3 grid, size_t smem, cudaStream_t s) {
+#define RLLM_SF(SP) \
+  return perch ? launch_ex(state_scan_fast_kernel<TB, SP, true>, grid, dim3(128), smem, s, 1, a) \
+               : launch_ex(state_scan_fast_kernel<TB, SP, false>, grid, dim3(128), smem, s, 1, a)
+  switch (split) {
+    case 1: RLLM_SF(1);
+    case 2: RLLM_SF(2);
+    case 4: RLLM_SF(4);
+    default: RLLM_SF(8);
+  }
+#undef RLLM_SF
+}
+
 }  // namespace
 
 RLLM_API int rllm_short_conv(int dt, const void* x, long long ld, int col0, int C, int taps, const float* w, const float* bias,
@@ -323,6 +448,14 @@ RLLM_API int rllm_state_scan(int beta_dt, const float* q, long long q_ld, int q_
                                        (size_t)a.ch * cols + 2 * a.ch);
   const dim3 grid(S, H, (vdim + cols - 1) / cols);
   cudaStream_t s = (cudaStream_t)stream;
+  if (dim == 32 * a.split && dim <= 256) {           // 32 channels a thread, sizes known to the compiler
+    const int ldk = a.split * 36;
+    const size_t fsmem = sizeof(float) * ((size_t)a.ch * ldk * (decay_per_channel ? 3 : 2) + (decay_per_channel ? 0 : a.ch) +
+                                          (size_t)a.ch * cols + 2 * a.ch);
+    if (beta == nullptr || beta_dt == DT_F32) return launch_scan_fast<float>(a, a.split, decay_per_channel != 0, grid, fsmem, s);
+    if (beta_dt == DT_BF16) return launch_scan_fast<bf16>(a, a.split, decay_per_channel != 0, grid, fsmem, s);
+    return ERR_BAD_DTYPE;
+  }
   const bool small = dim <= 16;
   if (beta == nullptr || beta_dt == DT_F32)
     return small ? launch_ex(state_scan_kernel<float, 16>, grid, dim3(128), smem, s, 1, a)

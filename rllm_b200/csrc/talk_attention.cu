@@ -13,9 +13,11 @@
 // talk_attention_simt: one CTA per query token, float arithmetic on the CUDA cores (the 32-bit run, and every size).
 //   Warp w owns the heads g with g % warps == w: their running maxima and sums in the first pass, their output
 //   columns (lane d, d + 32, ...) in the second. Keys and values of one kv head at a time pass through shared memory.
+// talk_attention_mma (talk_attention_mma.cuh): bfloat16 on the tensor cores, one pass, the mix after the values.
 // value_norm_store: keys as they are, values divided by their root mean square per head (no weight), into the pages.
 #include "common.cuh"
 using namespace rllm;
+#include "talk_attention_mma.cuh"
 
 namespace {
 

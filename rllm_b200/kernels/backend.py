@@ -435,8 +435,15 @@ class Backend:
             self._hy.value_norm_store(proj, k_off, v_off, nkv, kd, vd, eps, norm, cache.slots, cache.k, cache.v)
 
     def talk_attention(self, q, cache, ctx, nh, scale, mix, window, chunk, sinks):
-        """Attention whose heads' softmax weights are mixed by `mix` before they meet the values."""
-        return self._hy.talk_attention_simt(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, nh, scale,
+        """Attention whose heads' softmax weights are mixed by `mix` before they meet the values: bfloat16 on the
+        tensor cores where the kernel takes the sizes, else (and in the 32-bit run) in float on the CUDA cores."""
+        hy = self._hy
+        kd, vd = cache.k.shape[3], cache.v.shape[3]
+        if self.fast and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1" \
+                and hy.talk_mma_supported(q.dtype, nh, kd, vd, cache.page_size):
+            return hy.talk_attention_mma(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, ctx.cu_q,
+                                         ctx.num_seqs, ctx.max_q_len, nh, scale, mix, window, chunk, sinks)
+        return hy.talk_attention_simt(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, nh, scale,
                                             mix, window, chunk, sinks)
 
     # ---- selection

@@ -31,6 +31,9 @@ ops.register_signatures("hybrid", {
     "rllm_value_norm_store": [c_int, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P, _P, _P, c_int, _P],
     "rllm_talk_attention_simt": [c_int, _P, _LL, _P, _P, _P, _P, _P, _LL, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_int, c_int, _P],
+    "rllm_talk_attention_mma_supported": [c_int, c_int, c_int, c_int, c_int],
+    "rllm_talk_attention_mma": [_P, _LL, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_float, c_int, c_int, _P, _P, _P],
 })
 
 GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
@@ -315,4 +318,45 @@ def talk_attention_simt(q, kcache, vcache, token_seq, positions, block_table, nh
         _dt(q, "q"), q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), token_seq.data_ptr(), positions.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), mix.data_ptr(), _ptr(sinks), out.data_ptr(), T, nh, nkv, kd, vd, page_size,
         float(scale), int(window or 0), int(chunk or 0), _stream()), "talk_attention_simt")
+    return out
+
+
+def talk_mma_supported(dtype, nh, kd, vd, page_size) -> bool:
+    return bool(_fn("hybrid", "rllm_talk_attention_mma_supported")(_dt_of(dtype), nh, kd, vd, page_size))
+
+
+def _dt_of(dtype) -> int:
+    return {torch.float32: ops.DT_F32, torch.bfloat16: ops.DT_BF16}.get(dtype, -1)
+
+
+def talk_attention_mma(q, kcache, vcache, token_seq, positions, block_table, cu_q, num_seqs, max_q_len, nh, scale, mix,
+                       window=None, chunk=None, sinks=None) -> torch.Tensor:
+    """The same attention in bfloat16 on the tensor cores (`mma.sync`, float softmax). The mix is applied after the
+    values: a first kernel leaves, as floats, every head's weights summed over every kv head's values ([T, nh, nkv,
+    vd], one pass with a running softmax), a second one adds them by `mix` and rounds once. `cu_q` int32
+    [num_seqs + 1]: each sequence's rows; `max_q_len`: the longest portion of the step."""
+    _cuda(q, "q")
+    T = q.shape[0]
+    nkv = kcache.shape[1]
+    _caches(kcache, vcache, q.dtype, nkv)
+    _, _, page_size, kd = kcache.shape
+    vd = vcache.shape[3]
+    if q.dim() != 2 or q.stride(1) != 1 or q.shape[1] != nh * kd:
+        raise KernelError(f"q must be [T, {nh * kd}] with unit inner stride, got {list(q.shape)}")
+    if not talk_mma_supported(q.dtype, nh, kd, vd, page_size):
+        raise KernelError(f"talk_attention_mma: bfloat16 with head sizes in steps of 16 up to 128, got {q.dtype} {kd}/{vd}")
+    _i32(positions, "positions", T)
+    _i32(cu_q, "cu_q", num_seqs + 1)
+    if block_table.dtype != torch.int32 or block_table.dim() != 2 or block_table.stride(1) != 1:
+        raise KernelError("block_table must be int32 [sequences, pages] with unit inner stride")
+    _f32(mix, "head mix", (nh, nh))
+    if sinks is not None:
+        _f32(sinks, "sinks", (nh,))
+    parts = torch.empty((T, nh, nkv, vd), dtype=torch.float32, device=q.device)
+    out = torch.empty((T, nh * vd), dtype=q.dtype, device=q.device)
+    _check(_fn("hybrid", "rllm_talk_attention_mma")(
+        q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(), parts.data_ptr(), positions.data_ptr(),
+        cu_q.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(num_seqs), T, int(max_q_len), nh, nkv, kd, vd,
+        page_size, float(scale), int(window or 0), int(chunk or 0), mix.data_ptr(), _ptr(sinks), _stream()),
+        "talk_attention_mma", 2)
     return out

@@ -233,6 +233,60 @@ class OpProfile:
     def gla_finish(self, o, *a, **k):
         return self._timed("gla_finish", 2 * _nbytes(o), 0, self._be.gla_finish, o, *a, **k)
 
+    # ---- library "hybrid"
+    def pair_embed(self, ctx, table, *a, **k):
+        return self._timed("embed", ctx.token_ids.numel() * table.shape[1] * (2 * table.element_size() + 4), 0,
+                           self._be.pair_embed, ctx, table, *a, **k)
+
+    def combine(self, h, *outputs):
+        n = 2
+        for y in outputs:
+            n += len(y.terms) if hasattr(y, "terms") else 0 if y is None else 1
+        return self._timed("norm+add", n * _nbytes(h), 0, self._be.combine, h, *outputs)
+
+    def linear_glu(self, x, w_gate_up, act, limit=0.0, alpha=1.0):
+        return self._product("gate_up+act", x, w_gate_up, self._be.linear_glu, x, w_gate_up, act, limit, alpha)
+
+    def experts_glu_up(self, x, w_gate_up, plan, act, limit=0.0, alpha=1.0):
+        rows, (E, F2, K) = plan.n_rows, w_gate_up.shape
+        return self._timed("experts_up", _nbytes(w_gate_up) + rows * (K * 2 + F2 * 4 + F2), 2 * rows * F2 * K,
+                           self._be.experts_glu_up, x, w_gate_up, plan, act, limit, alpha)
+
+    def short_conv(self, x, col0, channels, *a, **k):
+        return self._timed("short_conv", x.shape[0] * channels * (x.element_size() + 4), 0, self._be.short_conv, x, col0,
+                           channels, *a, **k)
+
+    def unit_heads(self, x, col0, heads, dim, *a, **k):
+        return self._timed("scan_gates", x.shape[0] * heads * dim * 8, 0, self._be.unit_heads, x, col0, heads, dim, *a, **k)
+
+    def softplus_decay(self, z, col0, n, *a, **k):
+        return self._timed("scan_gates", z.shape[0] * n * (z.element_size() + 4), 0, self._be.softplus_decay, z, col0, n, *a, **k)
+
+    def state_scan(self, q, q_heads, k, k_heads, v, decay, heads, dim, vdim, ctx, state, beta=None, vscale=None, skip=None):
+        T = q.shape[0]
+        nbytes = T * (heads * (2 * dim + 2 * vdim) * 4) + _nbytes(decay) + 2 * ctx.num_seqs * heads * dim * vdim * 4
+        flops = (7 if beta is not None else 5) * T * heads * dim * vdim
+        return self._timed("state_scan", nbytes, flops, self._be.state_scan, q, q_heads, k, k_heads, v, decay, heads, dim,
+                           vdim, ctx, state, beta, vscale, skip)
+
+    def gated_norm(self, y, *a, **k):
+        return self._timed("gated_norm", _nbytes(y) * 7 // 4, 0, self._be.gated_norm, y, *a, **k)
+
+    def value_norm_store(self, proj, k_off, v_off, nkv, kd, vd, *a, **k):
+        return self._timed("value_norm", 2 * proj.shape[0] * nkv * (kd + vd) * proj.element_size(), 0,
+                           self._be.value_norm_store, proj, k_off, v_off, nkv, kd, vd, *a, **k)
+
+    def talk_attention(self, q, cache, ctx, nh, scale, mix, window, chunk, sinks):
+        kd, vd, nkv = cache.k.shape[3], cache.v.shape[3], cache.k.shape[1]
+        lens, qs = ctx.kv_lens_host, ctx.q_lens_host
+        if lens is None:
+            lens, qs = [ctx.max_kv_len] * ctx.num_seqs, [1] * ctx.num_seqs
+        seen = [min(L, window + n - 1) if window else L for L, n in zip(lens, qs)]
+        pairs = sum(n * (s - n) + n * (n + 1) // 2 for s, n in zip(seen, qs))
+        nbytes = sum(seen) * nkv * (kd + vd) * cache.k.element_size() + _nbytes(q) + q.shape[0] * nh * vd * q.element_size()
+        return self._timed("talk_attention", nbytes, 2 * nh * (kd + vd) * pairs, self._be.talk_attention, q, cache, ctx, nh,
+                           scale, mix, window, chunk, sinks)
+
     def argmax(self, logits):
         return self._timed("sample", _nbytes(logits), 0, self._be.argmax, logits)
 

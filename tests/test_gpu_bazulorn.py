@@ -5,6 +5,7 @@ would hide a fault the inputs are made so that it shows: the input at one positi
 wins every score it takes part in (a window's edge that is one off, a far key that is lost, the first tokens),
 scores are small enough for the sink to hold a visible share of every softmax, and decays are near one so that
 the first token is still felt at the end."""
+import itertools
 import os
 import subprocess
 import sys
@@ -350,6 +351,17 @@ def test_talk_attention_far_keys_in_long_contexts(window):
         got = hybrid.talk_attention_simt(qd, kc.to(DEV), vc.to(DEV), seq, pos, bt.to(DEV), nh, 0.11, mix.to(DEV), window, None,
                                          torch.zeros(nh, device=DEV))
         assert rel(got, want) < tol, dtype
+        if dtype == torch.bfloat16:          # the tensor-core kernel: decoded tokens and a portion in one launch, then tokens alone
+            assert hybrid.talk_mma_supported(dtype, nh, kd, vd, page)
+            cu = torch.tensor([0] + list(itertools.accumulate(qlens)), dtype=torch.int32, device=DEV)
+            got = hybrid.talk_attention_mma(qd, kc.to(DEV), vc.to(DEV), seq, pos, bt.to(DEV), cu, S, max(qlens), nh, 0.11,
+                                            mix.to(DEV), window, None, torch.zeros(nh, device=DEV))
+            assert rel(got, want) < tol
+            one = [0, 1, 42]
+            cu1 = torch.arange(4, dtype=torch.int32, device=DEV)
+            got1 = hybrid.talk_attention_mma(qd[one], kc.to(DEV), vc.to(DEV), seq[one], pos[one], bt[[0, 1, 3]].to(DEV), cu1, 3, 1,
+                                             nh, 0.11, mix.to(DEV), window, None, torch.zeros(nh, device=DEV))
+            assert rel(got1, want[one]) < tol
 
 
 # ------------------------------------------------------------------ the recurrent mixers, over steps and slots
@@ -394,11 +406,13 @@ RECURRENT = [
     ("ssm", B.ssm(6, 8, 12, 3, 1, 1)),             # one tap: no convolution state
     ("ssm", B.ssm(5, 6, 14, 5, 5, 5)),             # a group per head
     ("ssm", B.ssm(2, 64, 128, 1, 2, 4)),           # a large state
+    ("ssm", B.ssm(3, 20, 32, 3, 1, 2)),            # a warp's lanes a state
     ("delta", B.delta(4, 2, 20, 24, 4, 8, 12, None)["mixer"]),
     ("delta", B.delta(1, 1, 64, 72, 2, 16, 4, None)["mixer"]),
     ("delta", B.delta(6, 3, 8, 8, 5, 4, 20, None)["mixer"]),
     ("delta", B.delta(2, 2, 130, 20, 1, 8, 8, None)["mixer"]),     # key channels beyond a warp's lanes, one tap
     ("delta", B.delta(2, 1, 128, 128, 3, 8, 8, None)["mixer"]),    # a large state
+    ("delta", B.delta(2, 2, 256, 24, 2, 8, 8, None)["mixer"]),     # eight lanes a value column
 ]
 
 
