@@ -26,6 +26,15 @@ namespace {
 
 constexpr int MAX_TAPS = 8;
 
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem, bool pred) {      // pred false: zero
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem);
+  const int sz = pred ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gmem), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_0() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
@@ -116,7 +125,7 @@ struct ScanArgs {
   const void* beta; long long beta_ld;                // logits [T, H] of the projection's type, or null: plain form
   const float* vscale;                                // [T, H] or null
   const float* skip;                                  // [H] or null
-  int H, dim, vdim, split, ch;
+  int H, dim, vdim, split, ch, beta_bf16;
   const int* cu_q; const int* state_slots;
   float* state;                                       // [slots, H, dim, vdim]
   float* out;                                         // [T, H, vdim]
@@ -249,23 +258,21 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const TG* __restr
 
 inline unsigned blocks_for(long long n) { return (unsigned)((n + 255) / 256 > 65535 * 8 ? 65535 * 8 : (n + 255) / 256); }
 
-// The same recurrence for heads of 32 * SPLIT key channels (32, 64, 128, 256), the sizes known when compiled: a thread's
-// 32 channels are neighbours (sub * 32 ...), so queries, keys and decays come from shared memory in pieces of four
-// (rows padded by four floats a lane share, which keeps the shares on different banks), and the sums over channels
-// run as four chains side by side. Same ownership, same staging and, per position, the same order of sums
-// whatever the cut into steps.
-template <typename TB, int SPLIT, bool PERCH>
+// The same recurrence for heads of R * SPLIT key channels (32 to 256) with R = 32, 16 or 8 channels a thread, the sizes
+// known when compiled: a thread's channels are neighbours (sub * R ...), so queries, keys and decays come from shared
+// memory in pieces of four (rows padded by four floats a lane share, which keeps the shares on different banks),
+// and the sums over channels run as four chains side by side. Fewer channels a thread means fewer value columns a
+// CTA and more CTAs a head; R depends on the sizes alone, so a position's result is the same bits whatever the cut
+// into steps and whatever else is in the batch.
+template <int R, int SPLIT, bool PERCH>
 __global__ void __launch_bounds__(128) state_scan_fast_kernel(ScanArgs a) {
   pdl_launch();
   pdl_wait();
-  constexpr int R = 32, DIM = R * SPLIT, LDK = SPLIT * (R + 4), COLS = 128 / SPLIT;
+  constexpr int DIM = R * SPLIT, LDK = SPLIT * (R + 4), COLS = 128 / SPLIT;
   extern __shared__ __align__(16) float sm[];
   const int vdim = a.vdim, ch = a.ch, H = a.H;
-  float* qs = sm;                                    // [ch][LDK]
-  float* ks = qs + ch * LDK;
-  float* as = ks + ch * LDK;                         // [ch][LDK] or [ch]
-  float* vs = as + (PERCH ? ch * LDK : ch);          // [ch][COLS]
-  float* bs = vs + ch * COLS;                        // [ch] beta, [ch] vscale
+  // a stage: queries [ch][LDK], keys [ch][LDK], decays [ch][LDK] or [ch], values [ch][COLS], beta [ch], vscale [ch]
+  const int stg = (ch * LDK * (PERCH ? 3 : 2) + (PERCH ? 0 : ch) + ch * COLS + 2 * ch + 3) & ~3;
   const int seq = blockIdx.x, h = blockIdx.y;
   const int sub = threadIdx.x % SPLIT, col = threadIdx.x / SPLIT;
   const int v = blockIdx.z * COLS + col;
@@ -279,29 +286,69 @@ __global__ void __launch_bounds__(128) state_scan_fast_kernel(ScanArgs a) {
   for (int i = 0; i < R; ++i) S[i] = (slot >= 0 && vok) ? sp[(long long)i * vdim] : 0.f;
   const float skip = a.skip ? a.skip[h] : 0.f;
   const bool delta = a.beta != nullptr;
-  for (int c0 = row0; c0 < row1; c0 += ch) {
+  // The next tokens' rows travel into the other stage (cp.async, four bytes a copy: the columns of a view need no
+  // alignment) while this stage's tokens are worked on; the few numbers a token has per head (decay, beta, value
+  // scale) wait in registers of the first threads meanwhile.
+  auto issue = [&](int c0, int stage) {
+    float* qs = sm + stage * stg;
+    float* ks = qs + ch * LDK;
+    float* as = ks + ch * LDK;
+    float* vs = as + (PERCH ? ch * LDK : ch);
     const int n = min(ch, row1 - c0);
-    __syncthreads();
     for (int x = threadIdx.x; x < n * DIM; x += 128) {
       const int cc = x / DIM, k = x % DIM;
       const long long r = c0 + cc;
       const int at = cc * LDK + (k / R) * (R + 4) + k % R;
-      qs[at] = a.q[r * a.q_ld + qh * DIM + k];
-      ks[at] = a.k[r * a.k_ld + kh * DIM + k];
-      if (PERCH) as[at] = a.decay[(r * H + h) * DIM + k];
+      cp_async4(qs + at, a.q + r * a.q_ld + qh * DIM + k, true);
+      cp_async4(ks + at, a.k + r * a.k_ld + kh * DIM + k, true);
+      if (PERCH) cp_async4(as + at, a.decay + (r * H + h) * DIM + k, true);
     }
     for (int x = threadIdx.x; x < n * COLS; x += 128) {
-      const int cc = x / COLS, c = x % COLS;
-      const int vv = blockIdx.z * COLS + c;
-      vs[x] = vv < vdim ? a.v[(long long)(c0 + cc) * a.v_ld + h * vdim + vv] : 0.f;
+      const int cc = x / COLS, vv = blockIdx.z * COLS + x % COLS;
+      cp_async4(vs + x, a.v + (long long)(c0 + cc) * a.v_ld + h * vdim + (vv < vdim ? vv : 0), vv < vdim);
     }
-    for (int cc = threadIdx.x; cc < n; cc += 128) {
-      const long long r = c0 + cc;
-      if (!PERCH) as[cc] = a.decay[r * H + h];
-      bs[cc] = delta ? sigmoid_f(to_f32(reinterpret_cast<const TB*>(a.beta)[r * a.beta_ld + h])) : 1.f;
-      bs[ch + cc] = a.vscale ? a.vscale[r * H + h] : 1.f;
+  };
+  float n_al = 1.f, n_b = 0.f, n_vs = 1.f;
+  auto few_load = [&](int c0) {
+    if ((int)threadIdx.x < min(ch, row1 - c0)) {
+      const long long r = c0 + threadIdx.x;
+      if (!PERCH) n_al = a.decay[r * H + h];
+      if (delta) n_b = a.beta_bf16 ? to_f32(reinterpret_cast<const bf16*>(a.beta)[r * a.beta_ld + h])
+                                   : reinterpret_cast<const float*>(a.beta)[r * a.beta_ld + h];
+      if (a.vscale) n_vs = a.vscale[r * H + h];
     }
+  };
+  auto few_store = [&](int stage) {
+    if ((int)threadIdx.x < ch) {
+      float* as = sm + stage * stg + 2 * ch * LDK;
+      float* bs = as + (PERCH ? ch * LDK : ch) + ch * COLS;
+      if (!PERCH) as[threadIdx.x] = n_al;
+      bs[threadIdx.x] = delta ? sigmoid_f(n_b) : 1.f;
+      bs[ch + threadIdx.x] = n_vs;
+    }
+  };
+  const int chunks = (row1 - row0 + ch - 1) / ch;
+  if (chunks > 0) {
+    issue(row0, 0);
+    few_load(row0);
+    few_store(0);
+  }
+  cp_async_commit();
+  for (int ci = 0; ci < chunks; ++ci) {
+    const int c0 = row0 + ci * ch, stage = ci & 1;
+    const int n = min(ch, row1 - c0);
+    if (ci + 1 < chunks) {
+      issue(c0 + ch, stage ^ 1);
+      few_load(c0 + ch);
+    }
+    cp_async_commit();
+    cp_async_wait_1();
     __syncthreads();
+    const float* qs = sm + stage * stg;
+    const float* ks = qs + ch * LDK;
+    const float* as = ks + ch * LDK;
+    const float* vs = as + (PERCH ? ch * LDK : ch);
+    const float* bs = vs + ch * COLS;
     for (int cc = 0; cc < n; ++cc) {
       const float4* kr = reinterpret_cast<const float4*>(ks + cc * LDK + sub * (R + 4));
       const float4* qr = reinterpret_cast<const float4*>(qs + cc * LDK + sub * (R + 4));
@@ -353,25 +400,26 @@ __global__ void __launch_bounds__(128) state_scan_fast_kernel(ScanArgs a) {
       for (int w = 1; w < SPLIT; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
       if (sub == 0 && vok) a.out[((long long)(c0 + cc) * H + h) * vdim + v] = fmaf(skip, x, o);
     }
+    if (ci + 1 < chunks) few_store(stage ^ 1);
+    __syncthreads();            // this stage is free for the copy after the next
   }
+  cp_async_wait_0();
   if (slot >= 0 && vok) {
 #pragma unroll
     for (int i = 0; i < R; ++i) sp[(long long)i * vdim] = S[i];
   }
 }
 
-template <typename TB>
-int launch_scan_fast(const ScanArgs& a, int split, bool perch, dim3 grid, size_t smem, cudaStream_t s) {
-#define RLLM_SF(SP) \
-  return perch ? launch_ex(state_scan_fast_kernel<TB, SP, true>, grid, dim3(128), smem, s, 1, a) \
-               : launch_ex(state_scan_fast_kernel<TB, SP, false>, grid, dim3(128), smem, s, 1, a)
-  switch (split) {
-    case 1: RLLM_SF(1);
-    case 2: RLLM_SF(2);
-    case 4: RLLM_SF(4);
-    default: RLLM_SF(8);
-  }
+int launch_scan_fast(const ScanArgs& a, int r, bool perch, dim3 grid, size_t smem, cudaStream_t s) {
+#define RLLM_SF(RR, SP)                                                                                            \
+  if (r == RR && a.split == SP)                                                                                    \
+    return perch ? launch_ex(state_scan_fast_kernel<RR, SP, true>, grid, dim3(128), smem, s, 1, a)                 \
+                 : launch_ex(state_scan_fast_kernel<RR, SP, false>, grid, dim3(128), smem, s, 1, a)
+  RLLM_SF(32, 1); RLLM_SF(32, 2); RLLM_SF(32, 4); RLLM_SF(32, 8);
+  RLLM_SF(16, 2); RLLM_SF(16, 4); RLLM_SF(16, 8); RLLM_SF(16, 16);
+  RLLM_SF(8, 4); RLLM_SF(8, 8); RLLM_SF(8, 16); RLLM_SF(8, 32);
 #undef RLLM_SF
+  return ERR_BAD_SIZE;
 }
 
 }  // namespace
@@ -429,11 +477,21 @@ RLLM_API int rllm_state_scan_split(int dim) {
   return split;
 }
 
+// Channels a thread for the kernel with compiled sizes (0: the general kernel). 32 measured best for single tokens at
+// every batch (fewer channels a thread mean more CTAs that each stage a head's whole queries and keys) and within a
+// tenth of the best for one long prompt; `want` (16 or 8) asks for fewer, for measurements.
+static int scan_fast_channels(int dim, int want) {
+  if (dim != 32 && dim != 64 && dim != 128 && dim != 256) return 0;
+  int r = (want == 16 || want == 8) ? want : 32;
+  while (dim / r > 32) r <<= 1;
+  return r;
+}
+
 RLLM_API int rllm_state_scan(int beta_dt, const float* q, long long q_ld, int q_heads, const float* k, long long k_ld,
                              int k_heads, const float* v, long long v_ld, const float* decay, int decay_per_channel,
                              const void* beta, long long beta_ld, const float* vscale, const float* skip, int S, int H,
                              int dim, int vdim, const int* cu_q, const int* state_slots, float* state, float* out,
-                             void* stream) {
+                             int channels, void* stream) {
   if (S <= 0) return 0;
   if (H <= 0 || dim <= 0 || dim > 1024 || vdim <= 0 || q_heads <= 0 || k_heads <= 0 || H % q_heads || H % k_heads)
     return ERR_BAD_SIZE;
@@ -443,19 +501,22 @@ RLLM_API int rllm_state_scan(int beta_dt, const float* q, long long q_ld, int q_
   a.skip = skip; a.H = H; a.dim = dim; a.vdim = vdim; a.cu_q = cu_q; a.state_slots = state_slots; a.state = state; a.out = out;
   a.split = rllm_state_scan_split(dim);
   a.ch = dim <= 128 ? 16 : dim <= 256 ? 8 : dim <= 512 ? 4 : 2;
+  a.beta_bf16 = beta != nullptr && beta_dt == DT_BF16;
+  if (beta != nullptr && beta_dt != DT_BF16 && beta_dt != DT_F32) return ERR_BAD_DTYPE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (const int r = scan_fast_channels(dim, channels)) {
+    a.split = dim / r;
+    const int fcols = 128 / a.split, ldk = a.split * (r + 4);
+    a.ch = a.ch > 2 ? a.ch / 2 : 1;                  // two stages in the room of one
+    const size_t stage = ((size_t)a.ch * ldk * (decay_per_channel ? 3 : 2) + (decay_per_channel ? 0 : a.ch) +
+                          (size_t)a.ch * fcols + 2 * a.ch + 3) & ~(size_t)3;
+    const size_t fsmem = sizeof(float) * 2 * stage;
+    return launch_scan_fast(a, r, decay_per_channel != 0, dim3(S, H, (vdim + fcols - 1) / fcols), fsmem, s);
+  }
   const int cols = 128 / a.split;
   const size_t smem = sizeof(float) * ((size_t)a.ch * dim * (decay_per_channel ? 3 : 2) + (decay_per_channel ? 0 : a.ch) +
                                        (size_t)a.ch * cols + 2 * a.ch);
   const dim3 grid(S, H, (vdim + cols - 1) / cols);
-  cudaStream_t s = (cudaStream_t)stream;
-  if (dim == 32 * a.split && dim <= 256) {           // 32 channels a thread, sizes known to the compiler
-    const int ldk = a.split * 36;
-    const size_t fsmem = sizeof(float) * ((size_t)a.ch * ldk * (decay_per_channel ? 3 : 2) + (decay_per_channel ? 0 : a.ch) +
-                                          (size_t)a.ch * cols + 2 * a.ch);
-    if (beta == nullptr || beta_dt == DT_F32) return launch_scan_fast<float>(a, a.split, decay_per_channel != 0, grid, fsmem, s);
-    if (beta_dt == DT_BF16) return launch_scan_fast<bf16>(a, a.split, decay_per_channel != 0, grid, fsmem, s);
-    return ERR_BAD_DTYPE;
-  }
   const bool small = dim <= 16;
   if (beta == nullptr || beta_dt == DT_F32)
     return small ? launch_ex(state_scan_kernel<float, 16>, grid, dim3(128), smem, s, 1, a)

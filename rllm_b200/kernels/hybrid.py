@@ -26,7 +26,7 @@ ops.register_signatures("hybrid", {
     "rllm_softplus_decay": [c_int, _P, _LL, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P],
     "rllm_state_scan_split": [c_int],
     "rllm_state_scan": [c_int, _P, _LL, c_int, _P, _LL, c_int, _P, _LL, _P, c_int, _P, _LL, _P, _P, c_int, c_int, c_int,
-                        c_int, _P, _P, _P, _P, _P],
+                        c_int, _P, _P, _P, _P, c_int, _P],
     "rllm_gated_norm": [_P, _P, c_int, _LL, _P, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "rllm_value_norm_store": [c_int, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P, _P, _P, c_int, _P],
     "rllm_talk_attention_simt": [c_int, _P, _LL, _P, _P, _P, _P, _P, _LL, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
@@ -205,11 +205,12 @@ def softplus_decay(z, col0, n, bias, a_log, want_step=False):
 
 
 def state_scan(q, q_heads, k, k_heads, v, decay, heads, dim, vdim, cu_q, num_seqs, state_slots, state, beta=None, vscale=None,
-               skip=None) -> torch.Tensor:
+               skip=None, channels: int = 0) -> torch.Tensor:
     """See csrc/recurrent.cu. q [T, q_heads * dim], k [T, k_heads * dim], v [T, heads * vdim]: float32 views with unit
     inner stride; decay float32 [T, heads * dim] (per channel) or [T, heads]; beta: logits [T, heads] of the
     projection's type (delta rule) or None (plain); vscale float32 [T, heads]; skip float32 [heads].
-    -> float32 [T, heads, vdim]; `state` float32 [slots, heads, dim, vdim] is updated."""
+    -> float32 [T, heads, vdim]; `state` float32 [slots, heads, dim, vdim] is updated. `channels` (32, 16 or 8): key
+    channels a thread where the kernel with compiled sizes runs, for measurements; 0: chosen from the sizes."""
     T = q.shape[0]
     for t, n, c in ((q, "q", q_heads * dim), (k, "k", k_heads * dim), (v, "v", heads * vdim)):
         _rows(t, n, c)
@@ -236,7 +237,7 @@ def state_scan(q, q_heads, k, k_heads, v, decay, heads, dim, vdim, cu_q, num_seq
         _dt(beta, "beta") if beta is not None else 0, q.data_ptr(), q.stride(0), int(q_heads), k.data_ptr(), k.stride(0),
         int(k_heads), v.data_ptr(), v.stride(0), decay.data_ptr(), int(per_channel), _ptr(beta),
         beta.stride(0) if beta is not None else 0, _ptr(vscale), _ptr(skip), int(num_seqs), int(heads), int(dim), int(vdim),
-        cu_q.data_ptr(), _ptr(state_slots), state.data_ptr(), out.data_ptr(), _stream()), "state_scan")
+        cu_q.data_ptr(), _ptr(state_slots), state.data_ptr(), out.data_ptr(), int(channels), _stream()), "state_scan")
     return out
 
 

@@ -347,6 +347,58 @@ def cmd_sink(a) -> None:
     sm100.check_error(DEV)
 
 
+def cmd_talk(a) -> None:
+    """Attention with mixed heads: one prompt of T tokens, then B single tokens at context C."""
+    from . import hybrid
+    nh, nkv, kd, vd, page = a.heads, a.kv_heads, a.dim, a.vdim, a.page
+    bf = lambda *shape: torch.randn(*shape, device=DEV, dtype=torch.bfloat16)
+    mixm, sinks, scale = torch.randn(nh, nh, device=DEV) * 0.2 + torch.eye(nh, device=DEV), torch.zeros(nh, device=DEV), kd ** -0.5
+    for T in a.tokens:
+        bt, pos, seq, cu, pages = _paged(1, T, T, page)
+        kc, vc, q = bf(pages, nkv, page, kd), bf(pages, nkv, page, vd), bf(T, nh * kd)
+        pairs = sum(min(p + 1, a.window or p + 1) for p in range(T))
+        if a.simt:
+            fn = lambda: hybrid.talk_attention_simt(q, kc, vc, seq, pos, bt, nh, scale, mixm, a.window or None, None, sinks)
+        else:
+            fn = lambda: hybrid.talk_attention_mma(q, kc, vc, seq, pos, bt, cu, 1, T, nh, scale, mixm, a.window or None, None, sinks)
+        run([fn] * 2, a.plain, f"mixed-heads attention ({'CUDA cores' if a.simt else 'mma.sync'}) T={T} heads={nh}/{nkv} of {kd}/{vd}",
+            flops=2.0 * nh * (kd + vd) * pairs)
+        if a.plain:
+            return
+    for B in a.batch:
+        C = a.context
+        bt, pos, seq, cu, pages = _paged(B, C, 1, page)
+        copies = max(1, min(8, int(2e9 // (pages * nkv * page * (kd + vd) * 2))))
+        caches = [(bf(pages, nkv, page, kd), bf(pages, nkv, page, vd)) for _ in range(copies)]
+        q = bf(B, nh * kd)
+        keys = min(C, a.window or C)
+        run([(lambda c=c: hybrid.talk_attention_mma(q, c[0], c[1], seq, pos, bt, cu, B, 1, nh, scale, mixm, a.window or None, None,
+                                                    sinks)) for c in caches], 0,
+            f"mixed-heads attention (mma.sync) {B} x 1 token, {C} keys, heads={nh}/{nkv} of {kd}/{vd}",
+            nbytes=B * keys * nkv * (kd + vd) * 2)
+
+
+def cmd_scan(a) -> None:
+    """The recurrence over a per-request state, plain or delta rule: one prompt of T tokens, then B single tokens."""
+    from . import hybrid
+    H, d, v = a.heads, a.dim, a.vdim
+    cases = [(1, T) for T in a.tokens] + [(B, 1) for B in a.batch]
+    for batch, new in cases:
+        T = batch * new
+        q, k = torch.randn(T, H * d, device=DEV) * d ** -0.5, torch.nn.functional.normalize(torch.randn(T, H, d, device=DEV), dim=-1).view(T, H * d)
+        x = torch.randn(T, H * v, device=DEV)
+        decay = torch.rand(T, H * d if a.delta else H, device=DEV) * 0.1 + 0.9
+        beta = torch.randn(T, H, device=DEV, dtype=torch.bfloat16) if a.delta else None
+        cu = (torch.arange(batch + 1, dtype=torch.int32) * new).to(DEV)
+        slots = torch.arange(batch, dtype=torch.int32).to(DEV)
+        states = [torch.zeros(batch, H, d, v, device=DEV) for _ in range(a.copies if new == 1 else 1)]
+        run([lambda s=s: hybrid.state_scan(q, H, k, H, x, decay, H, d, v, cu, batch, slots, s, beta, channels=a.channels) for s in states], a.plain,
+            f"state scan ({'delta rule' if a.delta else 'plain'}) {batch} x {new} tokens, {H} heads of {d} x {v}",
+            T * H * (2 * d + 2 * v) * 4 + decay.numel() * 4 + 2 * batch * H * d * v * 4, (7.0 if a.delta else 5.0) * T * H * d * v)
+        if a.plain:
+            return
+
+
 def main(argv=None) -> int:
     ints = lambda s: [int(x) for x in s.split(",")]
     ap = argparse.ArgumentParser(prog="python -m rllm_b200.kernels.microbench", description=__doc__.split("\n\n")[0])
@@ -388,6 +440,21 @@ def main(argv=None) -> int:
     for k, v in (("heads", 32), ("kv-heads", 8), ("dim", 64), ("vdim", 32), ("page", 16), ("context", 1024), ("chunk", 0),
                  ("width", 2048)):
         p.add_argument("--" + k, type=int, default=v)
+    p = sub.add_parser("talk")
+    p.add_argument("--plain", type=int, default=0, help="N plain launches of the prompt kernel instead of timing")
+    p.add_argument("--tokens", type=ints, default=[2048])
+    p.add_argument("--batch", type=ints, default=[8, 64])
+    p.add_argument("--simt", action="store_true", help="the CUDA-core kernel (prompts only)")
+    for k, v in (("heads", 16), ("kv-heads", 4), ("dim", 128), ("vdim", 128), ("page", 16), ("context", 1024), ("window", 0)):
+        p.add_argument("--" + k, type=int, default=v)
+    p = sub.add_parser("scan")
+    p.add_argument("--plain", type=int, default=0)
+    p.add_argument("--copies", type=int, default=8)
+    p.add_argument("--tokens", type=ints, default=[2048])
+    p.add_argument("--batch", type=ints, default=[8, 64])
+    p.add_argument("--delta", action="store_true", help="the delta rule with a decay per channel (default: plain, a decay per head)")
+    for k, v in (("heads", 16), ("dim", 128), ("vdim", 128), ("channels", 0)):
+        p.add_argument("--" + k, type=int, default=v)
     for name in ("gemm", "attn-decode", "attn-prefill"):
         p = sub.add_parser(name)
         p.add_argument("--plain", type=int, default=0, help="N plain launches instead of timing")
@@ -424,7 +491,8 @@ def main(argv=None) -> int:
         print("microbench: no CUDA device", file=sys.stderr)
         return 1
     {"gemm": cmd_gemm, "attn-decode": cmd_attn_decode, "attn-prefill": cmd_attn_prefill, "sample": cmd_sample,
-     "experts": cmd_experts, "latent-attn": cmd_latent_attn, "gla": cmd_gla, "sink": cmd_sink}[a.cmd](a)
+     "experts": cmd_experts, "latent-attn": cmd_latent_attn, "gla": cmd_gla, "sink": cmd_sink, "talk": cmd_talk,
+     "scan": cmd_scan}[a.cmd](a)
     return 0
 
 
