@@ -38,30 +38,30 @@ __device__ __forceinline__ void cp_async_wait_0() { asm volatile("cp.async.wait_
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
+// A CTA a token (blockIdx.x) and 256 channels (blockIdx.y): what a token has of its own is read once a thread.
 template <typename TI>
 __global__ void short_conv_kernel(const TI* __restrict__ x, long long ld, int col0, int C, int taps,
                                   const float* __restrict__ w, const float* __restrict__ bias,
                                   const int* __restrict__ token_seq, const int* __restrict__ positions,
                                   const int* __restrict__ cu_q, const int* __restrict__ state_slots,
-                                  const float* __restrict__ tail, float* __restrict__ out, long long n, int silu) {
+                                  const float* __restrict__ tail, float* __restrict__ out, int silu) {
   pdl_launch();
   pdl_wait();
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const int t = (int)(i / C), c = (int)(i % C);
-    const int s = token_seq[t], row0 = cu_q[s], pos = positions[t];
-    const int slot = state_slots ? state_slots[s] : -1;
-    float acc = bias ? bias[c] : 0.f;
-    for (int j = 0; j < taps; ++j) {
-      const int back = taps - 1 - j;
-      if (pos - back < 0) continue;
-      const int r = t - back;
-      float v = 0.f;
-      if (r >= row0) v = to_f32(x[(long long)r * ld + col0 + c]);
-      else if (slot >= 0) v = tail[((long long)slot * (taps - 1) + (taps - 1 - (row0 - r))) * C + c];
-      acc = fmaf(w[(long long)c * taps + j], v, acc);
-    }
-    out[i] = silu ? acc / (1.f + expf(-acc)) : acc;
+  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int s = token_seq[t], row0 = cu_q[s], pos = positions[t];
+  const int slot = state_slots ? state_slots[s] : -1;
+  float acc = bias ? bias[c] : 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int back = taps - 1 - j;
+    if (pos - back < 0) continue;
+    const int r = t - back;
+    float v = 0.f;
+    if (r >= row0) v = to_f32(x[(long long)r * ld + col0 + c]);
+    else if (slot >= 0) v = tail[((long long)slot * (taps - 1) + (taps - 1 - (row0 - r))) * C + c];
+    acc = fmaf(w[(long long)c * taps + j], v, acc);
   }
+  out[(long long)t * C + c] = silu ? acc / (1.f + expf(-acc)) : acc;
 }
 
 template <typename TI>
@@ -430,14 +430,16 @@ RLLM_API int rllm_short_conv(int dt, const void* x, long long ld, int col0, int 
   if (T <= 0 || C <= 0) return 0;
   if (taps < 1 || taps > MAX_TAPS) return ERR_BAD_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
-  const long long n = (long long)T * C;
+  const int threads = C >= 256 ? 256 : C >= 128 ? 128 : 64;
+  const dim3 grid((unsigned)T, (unsigned)((C + threads - 1) / threads));
+  if (grid.y > 65535) return ERR_TOO_LARGE;
   int rc;
   if (dt == DT_F32)
-    rc = launch_ex(short_conv_kernel<float>, dim3(blocks_for(n)), dim3(256), 0, s, 1, (const float*)x, ld, col0, C, taps, w, bias,
-                   token_seq, positions, cu_q, state_slots, (const float*)tail, out, n, silu);
+    rc = launch_ex(short_conv_kernel<float>, grid, dim3(threads), 0, s, 1, (const float*)x, ld, col0, C, taps, w, bias,
+                   token_seq, positions, cu_q, state_slots, (const float*)tail, out, silu);
   else if (dt == DT_BF16)
-    rc = launch_ex(short_conv_kernel<bf16>, dim3(blocks_for(n)), dim3(256), 0, s, 1, (const bf16*)x, ld, col0, C, taps, w, bias,
-                   token_seq, positions, cu_q, state_slots, (const float*)tail, out, n, silu);
+    rc = launch_ex(short_conv_kernel<bf16>, grid, dim3(threads), 0, s, 1, (const bf16*)x, ld, col0, C, taps, w, bias,
+                   token_seq, positions, cu_q, state_slots, (const float*)tail, out, silu);
   else return ERR_BAD_DTYPE;
   if (rc || taps == 1 || state_slots == nullptr || tail == nullptr) return rc;
   const unsigned blocks = (unsigned)(((long long)S * C + 255) / 256);

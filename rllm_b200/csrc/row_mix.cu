@@ -11,6 +11,8 @@
 // glu_act: out[r, f] = act(gate, up) of in[r, f] and in[r, F + f]:
 //   0: silu(g) * u     1: gelu_tanh(g) * u     2: g' = min(g, limit), u' = clamp(u, -limit, limit),
 //                                                 g' * sigmoid(alpha g') * (u' + 1)
+#include <cstdint>
+#include <initializer_list>
 #include "common.cuh"
 using namespace rllm;
 
@@ -79,37 +81,82 @@ __global__ void pair_embed_keep_kernel(const int* __restrict__ ids, const int* _
   if (slot >= 0 && cu_q[s + 1] > cu_q[s]) prev_state[slot] = ids[cu_q[s + 1] - 1];
 }
 
+// VEC 4: rows of a multiple of four numbers, read in 16-byte pieces (every row then starts on a 16-byte boundary).
+template <int VEC>
 __global__ void combine_kernel(float* __restrict__ h, const float* __restrict__ n0, const float* __restrict__ w0,
                                const float* __restrict__ n1, const float* __restrict__ w1, float coef, float eps,
                                const float* __restrict__ p0, int parts0, const float* __restrict__ p1, int parts1,
                                const float* __restrict__ p2, int parts2, int H) {
   pdl_launch();
   pdl_wait();
+  struct V { float v[VEC]; };
+  auto ld = [](const float* p) {
+    V r;
+    if (VEC == 4) { const float4 t = *reinterpret_cast<const float4*>(p); r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; }
+    else r.v[0] = *p;
+    return r;
+  };
   __shared__ float red[32];
   const size_t t = blockIdx.x;
   float r0 = 0.f, r1 = 0.f;
   if (n0) {
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = n0[t * H + i]; ss = fmaf(v, v, ss); }
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+      const V x = ld(n0 + t * H + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) ss = fmaf(x.v[e], x.v[e], ss);
+    }
     r0 = coef / sqrtf(block_sum(ss, red) / (float)H + eps);
   }
   if (n1) {
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = n1[t * H + i]; ss = fmaf(v, v, ss); }
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+      const V x = ld(n1 + t * H + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) ss = fmaf(x.v[e], x.v[e], ss);
+    }
     r1 = coef / sqrtf(block_sum(ss, red) / (float)H + eps);
   }
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float mix = 0.f, ff = 0.f;
-    if (n0) mix = n0[t * H + i] * r0 * w0[i];
-    if (n1) mix += n1[t * H + i] * r1 * w1[i];
-    auto sum = [&](const float* p, int parts) {
-      float m = 0.f;
-      if (p) { const float* r = p + t * parts * H + i; for (int k = 0; k < parts; ++k) m += r[(size_t)k * H]; }
-      return m;
+  for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+    V mix, ff;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) mix.v[e] = ff.v[e] = 0.f;
+    if (n0) {
+      const V x = ld(n0 + t * H + i), w = ld(w0 + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) mix.v[e] = x.v[e] * r0 * w.v[e];
+    }
+    if (n1) {
+      const V x = ld(n1 + t * H + i), w = ld(w1 + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) mix.v[e] += x.v[e] * r1 * w.v[e];
+    }
+    auto sum = [&](const float* p, int parts, V& acc) {       // parts in their order, then added to acc
+      if (!p) return;
+      V m;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) m.v[e] = 0.f;
+      const float* r = p + t * parts * H + i;
+      for (int k = 0; k < parts; ++k) {
+        const V x = ld(r + (size_t)k * H);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) m.v[e] += x.v[e];
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc.v[e] += m.v[e];
     };
-    mix += sum(p0, parts0);
-    ff = sum(p1, parts1) + sum(p2, parts2);
-    h[t * H + i] += mix + ff;
+    sum(p0, parts0, mix);
+    V f1, f2;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) f1.v[e] = f2.v[e] = 0.f;
+    sum(p1, parts1, f1);
+    sum(p2, parts2, f2);
+    const V hv = ld(h + t * H + i);
+    float out[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) out[e] = hv.v[e] + (mix.v[e] + (f1.v[e] + f2.v[e]));
+    if (VEC == 4) *reinterpret_cast<float4*>(h + t * H + i) = make_float4(out[0], out[1], out[2], out[3]);
+    else h[t * H + i] = out[0];
   }
 }
 
@@ -176,7 +223,14 @@ RLLM_API int rllm_combine(float* h, const float* n0, const float* w0, const floa
   if (T <= 0) return 0;
   if ((n0 && !w0) || (n1 && !w1)) return ERR_BAD_SIZE;
   const int threads = H >= 1024 ? 256 : 128;
-  return launch_ex(combine_kernel, dim3(T), dim3(threads), 0, (cudaStream_t)stream, 1, h, n0, w0, n1, w1, coef, eps, p0, parts0,
+  bool aligned = H % 4 == 0;
+  for (const void* q : {(const void*)h, (const void*)n0, (const void*)w0, (const void*)n1, (const void*)w1, (const void*)p0,
+                        (const void*)p1, (const void*)p2})
+    aligned = aligned && (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+  if (aligned)
+    return launch_ex(combine_kernel<4>, dim3(T), dim3(threads), 0, (cudaStream_t)stream, 1, h, n0, w0, n1, w1, coef, eps, p0,
+                     parts0, p1, parts1, p2, parts2, H);
+  return launch_ex(combine_kernel<1>, dim3(T), dim3(threads), 0, (cudaStream_t)stream, 1, h, n0, w0, n1, w1, coef, eps, p0, parts0,
                    p1, parts1, p2, parts2, H);
 }
 
