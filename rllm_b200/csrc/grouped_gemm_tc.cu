@@ -32,7 +32,17 @@ struct TcArgs {
   const int* tiles; const int* n_tiles;
   const int* rows_out; const float* row_scale;
   int* err;
+  int act; float limit, alpha;     // the gated epilogue: 0 silu(g) u, 1 gelu_tanh(g) u, 2 g' sigmoid(alpha g') (u' + 1), clamped
 };
+
+// act(g, u) of the gated epilogue, in float.
+__device__ __forceinline__ float gated_act(float g, float u, int act, float limit, float alpha) {
+  if (act == 0) return g / (1.f + __expf(-g)) * u;
+  if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
 
 template <int EPI>
 __global__ void __launch_bounds__(192)
@@ -149,7 +159,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             for (int q = 0; q < 4; ++q) {
               const float g0 = __uint_as_float(v[j + 2 * q]) * f, g1 = __uint_as_float(v[j + 2 * q + 1]) * f;
               const float u0 = __uint_as_float(v[16 + j + 2 * q]) * f, u1 = __uint_as_float(v[16 + j + 2 * q + 1]) * f;
-              __nv_bfloat162 h = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+              __nv_bfloat162 h = __floats2bfloat162_rn(gated_act(g0, u0, p.act, p.limit, p.alpha), gated_act(g1, u1, p.act, p.limit, p.alpha));
               o[q] = *reinterpret_cast<uint32_t*>(&h);
             }
             *reinterpret_cast<uint4*>(c + j) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -241,10 +251,13 @@ RLLM_API int rllm_grouped_gemm_tc_supported(long long lda, int N, int K) {
 // A: bfloat16 [a_rows, K], row stride lda: the plan's sorted rows. W: bfloat16 [E, N, K]. The plan (tiles of up to 128
 // rows) as for rllm_grouped_gemm_ragged. epi 2: C bfloat16 [a_rows, N] = relu(.)^2 in sorted order; epi 1: C float,
 // row rows_out[r] = row_scale[r] * (.); epi 3: W's rows in blocks of 16 gate rows and their 16 up rows (N a multiple
-// of 32), C bfloat16 [a_rows, N / 2] = silu(f g) * (f u) with f = row_scale[r]. err: one int on the device for a wait that ran out, or null.
+// of 32), C bfloat16 [a_rows, N / 2] = act(f g, f u) with f = row_scale[r] (1 without) and act by `act`, `limit`, `alpha`:
+// 0 silu(g) u, 1 gelu_tanh(g) u, 2 g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+// err: one int on the device for a wait that ran out, or null.
 RLLM_API int rllm_grouped_gemm_tc(int epi, const void* A, long long lda, long long a_rows, const void* W, int E, int N,
                                   int K, void* C, long long ldc, const int* tiles, const int* n_tiles, int max_tiles,
-                                  const int* rows_out, const float* row_scale, int* err, void* stream) {
+                                  const int* rows_out, const float* row_scale, int* err, int act, float limit, float alpha,
+                                  void* stream) {
   if (max_tiles <= 0 || a_rows <= 0) return 0;
   if (!rllm_grouped_gemm_tc_supported(lda, N, K) || !tiles || !n_tiles || E <= 0) return ERR_BAD_SIZE;
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)C & 15) || ldc % 8) return ERR_BAD_ALIGN;
@@ -252,7 +265,8 @@ RLLM_API int rllm_grouped_gemm_tc(int epi, const void* A, long long lda, long lo
   if (get_encoder()) return -5;
   CUtensorMap ma, mw;
   if (make_map(&ma, A, a_rows, K, lda) || make_map(&mw, W, (long long)E * N, K, K)) return -5;
-  TcArgs p = {C, ldc, N, K, tiles, n_tiles, rows_out, row_scale, err};
+  if (act < 0 || act > 2) return ERR_BAD_SIZE;
+  TcArgs p = {C, ldc, N, K, tiles, n_tiles, rows_out, row_scale, err, act, limit, alpha};
   dim3 grid((N + TN - 1) / TN, max_tiles, 1);
   if (epi == TEPI_RELU2) return launch_tc<TEPI_RELU2>(ma, mw, p, grid, (cudaStream_t)stream);
   if (epi == TEPI_F32) return launch_tc<TEPI_F32>(ma, mw, p, grid, (cudaStream_t)stream);

@@ -162,13 +162,15 @@ __global__ void combine_kernel(float* __restrict__ h, const float* __restrict__ 
 
 template <typename TI, typename TO>
 __global__ void glu_act_kernel(const TI* __restrict__ in, long long ld, TO* __restrict__ out, int F, long long n, int kind,
-                               float limit, float alpha) {
+                               float limit, float alpha, int block) {
   pdl_launch();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / F;
     const int f = (int)(i % F);
-    float g = to_f32(in[r * ld + f]), u = to_f32(in[r * ld + F + f]);
+    // gate columns then up columns, or blocks of `block` gate columns each followed by their up columns
+    const int gc = block ? f / block * 2 * block + f % block : f, uc = block ? gc + block : F + f;
+    float g = to_f32(in[r * ld + gc]), u = to_f32(in[r * ld + uc]);
     float y;
     if (kind == 0) {
       y = g / (1.f + expf(-g)) * u;
@@ -235,18 +237,18 @@ RLLM_API int rllm_combine(float* h, const float* n0, const float* w0, const floa
 }
 
 RLLM_API int rllm_glu_act(const void* in, int in_dt, long long ld, void* out, int out_dt, int R, int F, int kind, float limit,
-                          float alpha, void* stream) {
+                          float alpha, int block, void* stream) {
   if (R <= 0 || F <= 0) return 0;
-  if (kind < 0 || kind > 2) return ERR_BAD_SIZE;
+  if (kind < 0 || kind > 2 || block < 0 || (block && F % block)) return ERR_BAD_SIZE;
   const long long n = (long long)R * F;
   cudaStream_t s = (cudaStream_t)stream;
   const dim3 g(blocks_for(n)), b(256);
   if (in_dt == DT_F32 && out_dt == DT_F32)
-    return launch_ex(glu_act_kernel<float, float>, g, b, 0, s, 1, (const float*)in, ld, (float*)out, F, n, kind, limit, alpha);
+    return launch_ex(glu_act_kernel<float, float>, g, b, 0, s, 1, (const float*)in, ld, (float*)out, F, n, kind, limit, alpha, block);
   if (in_dt == DT_F32 && out_dt == DT_BF16)
-    return launch_ex(glu_act_kernel<float, bf16>, g, b, 0, s, 1, (const float*)in, ld, (bf16*)out, F, n, kind, limit, alpha);
+    return launch_ex(glu_act_kernel<float, bf16>, g, b, 0, s, 1, (const float*)in, ld, (bf16*)out, F, n, kind, limit, alpha, block);
   if (in_dt == DT_BF16 && out_dt == DT_BF16)
-    return launch_ex(glu_act_kernel<bf16, bf16>, g, b, 0, s, 1, (const bf16*)in, ld, (bf16*)out, F, n, kind, limit, alpha);
+    return launch_ex(glu_act_kernel<bf16, bf16>, g, b, 0, s, 1, (const bf16*)in, ld, (bf16*)out, F, n, kind, limit, alpha, block);
   return ERR_BAD_DTYPE;
 }
 

@@ -398,17 +398,25 @@ class Backend:
             return self.linear_swiglu(x, w_gate_up)
         return self._hy.glu_act(self.linear_f32(x, w_gate_up, tag="gate_up"), self.dtype, act, limit, alpha)
 
-    def experts_glu_up(self, x, w_gate_up, plan, act, limit=0.0, alpha=1.0):
+    def experts_glu_up(self, x, w_gate_up, plan, act, limit=0.0, alpha=1.0, block=None):
         """act(g, u) for every sorted row of the plan, g and u the row's token times the gate and the up rows of the
-        row's expert. W [E, 2F, K]: an expert's gate rows, then its up rows."""
-        gu = torch.empty((plan.n_rows, w_gate_up.shape[1]), dtype=torch.float32, device=x.device)
+        row's expert. W [E, 2F, K]: an expert's gate rows, then its up rows (`block` None), or blocks of `block` gate
+        rows each followed by their up rows (16: the tcgen05 kernel then activates in its epilogue)."""
+        F2 = w_gate_up.shape[1]
         if self._tc_experts(x, w_gate_up, plan):
             rows = self._mix.gather_rows_bf16(x, plan.rows_tok)
+            if block == 16:
+                out = torch.empty((plan.n_rows, F2 // 2), dtype=torch.bfloat16, device=x.device)
+                return self._mix.grouped_gemm_tc(rows, w_gate_up, plan, out, self._mix.GEPI_SILU_GATED,
+                                                 err=self._sm100.init(self.device).err, act=self._hy.GLU_ACTS[act],
+                                                 limit=limit, alpha=alpha)
+            gu = torch.empty((plan.n_rows, F2), dtype=torch.float32, device=x.device)
             self._mix.grouped_gemm_tc(rows, w_gate_up, plan, gu, self._mix.GEPI_STORE_F32,
                                       err=self._sm100.init(self.device).err)
         else:
+            gu = torch.empty((plan.n_rows, F2), dtype=torch.float32, device=x.device)
             self._mix.grouped_gemm_ragged(x, w_gate_up, plan, gu, self._mix.GEPI_STORE_F32, gather=True)
-        return self._hy.glu_act(gu, x.dtype, act, limit, alpha)
+        return self._hy.glu_act(gu, x.dtype, act, limit, alpha, block)
 
     def add_bias_f32(self, y, bias):
         return self._hy.add_bias_f32(y, bias)

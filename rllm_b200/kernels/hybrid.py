@@ -19,7 +19,7 @@ ops.register_signatures("hybrid", {
     "rllm_pair_embed": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, _LL, _LL,
                         _P, _P],
     "rllm_combine": [_P, _P, _P, _P, _P, c_float, c_float, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, _P],
-    "rllm_glu_act": [_P, c_int, _LL, _P, c_int, c_int, c_int, c_int, c_float, c_float, _P],
+    "rllm_glu_act": [_P, c_int, _LL, _P, c_int, c_int, c_int, c_int, c_float, c_float, c_int, _P],
     "rllm_add_bias_f32": [_P, _P, c_int, c_int, _P],
     "rllm_short_conv": [c_int, _P, _LL, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P],
     "rllm_unit_heads": [_P, _LL, c_int, c_int, c_int, c_float, c_float, c_int, _P],
@@ -119,8 +119,9 @@ def combine(h, normed=(), coef=1.0, eps=1e-6, plain=()) -> torch.Tensor:
     return h
 
 
-def glu_act(gu, out_dtype, act: str, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
-    """gu [R, 2F] (gate columns, then up columns; float32 or the run's type) -> [R, F] of `out_dtype`:
+def glu_act(gu, out_dtype, act: str, limit: float = 0.0, alpha: float = 1.0, block: int | None = None) -> torch.Tensor:
+    """gu [R, 2F] (gate columns, then up columns, or with `block` blocks of that many gate columns each followed by
+    their up columns; float32 or the run's type) -> [R, F] of `out_dtype`:
     "silu": silu(g) u; "gelu_tanh": gelu(g) u in its tanh form; "swish_clamped": with g' = min(g, limit) and
     u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1)."""
     if act not in GLU_ACTS:
@@ -131,7 +132,7 @@ def glu_act(gu, out_dtype, act: str, limit: float = 0.0, alpha: float = 1.0) -> 
         raise KernelError("gate/up rows must hold an even number of columns")
     out = torch.empty((R, F), dtype=out_dtype, device=gu.device)
     _check(_fn("hybrid", "rllm_glu_act")(gu.data_ptr(), _dt(gu, "gate/up"), gu.stride(0), out.data_ptr(), _dt(out, "out"), R, F,
-                                         GLU_ACTS[act], float(limit), float(alpha), _stream()), "glu_act")
+                                         GLU_ACTS[act], float(limit), float(alpha), int(block or 0), _stream()), "glu_act")
     return out
 
 

@@ -24,7 +24,8 @@ ops.register_signatures("experts", {
                                  _P],
     "rllm_grouped_gemm_tile_rows": [c_int, _LL, c_int, c_int],
     "rllm_grouped_gemm_tc_supported": [_LL, c_int, c_int],
-    "rllm_grouped_gemm_tc": [c_int, _P, _LL, _LL, _P, c_int, c_int, c_int, _P, _LL, _P, _P, c_int, _P, _P, _P, _P],
+    "rllm_grouped_gemm_tc": [c_int, _P, _LL, _LL, _P, c_int, c_int, c_int, _P, _LL, _P, _P, c_int, _P, _P, _P, c_int, c_float,
+                             c_float, _P],
     "rllm_gather_rows_bf16": [_P, _LL, _P, _P, c_int, c_int, _P],
     "rllm_moe_topk": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "rllm_moe_plan": [_P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
@@ -209,12 +210,13 @@ def gather_rows_bf16(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
 
 
 def grouped_gemm_tc(a: torch.Tensor, w: torch.Tensor, plan: RoutePlan, out: torch.Tensor, epilogue: int,
-                    scatter: bool = False, scale: bool = False, err: torch.Tensor | None = None) -> torch.Tensor:
+                    scatter: bool = False, scale: bool = False, err: torch.Tensor | None = None, act: int = 0,
+                    limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """The ragged product on tcgen05 (csrc/grouped_gemm_tc.cu): a [plan rows, K] bfloat16 in sorted order (no
     gather: see gather_rows_bf16), w [E, N, K]; epilogue GEPI_RELU2 (bfloat16 out, sorted order),
     GEPI_STORE_F32 (float out, `scatter` to the rows' places, `scale` by their weights) or GEPI_SILU_GATED (w's
-    rows in blocks of 16 gate rows and their 16 up rows; bfloat16 out [rows, N / 2] = silu(f g) * (f u), f the
-    row's weight with `scale`). The plan must have tiles of 128 rows. `err`: one int32 on the device that records a bounded wait that ran out."""
+    rows in blocks of 16 gate rows and their 16 up rows; bfloat16 out [rows, N / 2] = act(f g, f u), f the
+    row's weight with `scale`; `act` 0 silu(g) u, 1 gelu_tanh(g) u, 2 the clamped swish with `limit` and `alpha`). The plan must have tiles of 128 rows. `err`: one int32 on the device that records a bounded wait that ran out."""
     E, N, K = w.shape
     _rows(a, "a", K)
     _rows(out, "out", N // 2 if epilogue == GEPI_SILU_GATED else N)
@@ -229,7 +231,8 @@ def grouped_gemm_tc(a: torch.Tensor, w: torch.Tensor, plan: RoutePlan, out: torc
     _check(_fn("experts", "rllm_grouped_gemm_tc")(
         epilogue, a.data_ptr(), a.stride(0), plan.n_rows, w.data_ptr(), E, N, K, out.data_ptr(), out.stride(0),
         plan.tiles.data_ptr(), plan.n_tiles.data_ptr(), plan.max_tiles, plan.rows_dest.data_ptr() if scatter else None,
-        plan.rows_scale.data_ptr() if scale else None, _ptr(err), _stream()), "grouped_gemm_tc")
+        plan.rows_scale.data_ptr() if scale else None, _ptr(err), int(act), float(limit), float(alpha), _stream()),
+        "grouped_gemm_tc")
     return out
 
 

@@ -247,10 +247,10 @@ class OpProfile:
     def linear_glu(self, x, w_gate_up, act, limit=0.0, alpha=1.0):
         return self._product("gate_up+act", x, w_gate_up, self._be.linear_glu, x, w_gate_up, act, limit, alpha)
 
-    def experts_glu_up(self, x, w_gate_up, plan, act, limit=0.0, alpha=1.0):
+    def experts_glu_up(self, x, w_gate_up, plan, act, limit=0.0, alpha=1.0, block=None):
         rows, (E, F2, K) = plan.n_rows, w_gate_up.shape
         return self._timed("experts_up", _nbytes(w_gate_up) + rows * (K * 2 + F2 * 4 + F2), 2 * rows * F2 * K,
-                           self._be.experts_glu_up, x, w_gate_up, plan, act, limit, alpha)
+                           self._be.experts_glu_up, x, w_gate_up, plan, act, limit, alpha, block)
 
     def short_conv(self, x, col0, channels, *a, **k):
         return self._timed("short_conv", x.shape[0] * channels * (x.element_size() + 4), 0, self._be.short_conv, x, col0,

@@ -154,8 +154,15 @@ class GluRoutedExperts(Part):
         return ps
 
     def finalize(self, device, dtype):
-        self._gate_up = self.w_gate_up.view(self.experts, 2 * self.ff, self.hidden)
-        self._down = self.w_down.view(self.experts, self.hidden, self.ff)
+        E, F, W = self.experts, self.ff, self.hidden
+        self._block = 16 if F % 16 == 0 else None
+        if self._block and getattr(self, "_arranged", None) is not self.w_gate_up:
+            # blocks of 16 gate rows each followed by their 16 up rows (as in GatedRoutedExperts): a tile of the
+            # product then holds both halves of its outputs and the kernel activates in its epilogue
+            gu = self.w_gate_up.view(E, 2, F // 16, 16, W).permute(0, 2, 1, 3, 4).contiguous()
+            self.w_gate_up = self._arranged = gu.view(E * 2 * F, W)
+        self._gate_up = self.w_gate_up.view(E, 2 * F, W)
+        self._down = self.w_down.view(E, W, F)
         self._bias = None if self.b_router is None else self.b_router.float().contiguous()
 
     def forward(self, x, ctx, residual=None):
@@ -166,7 +173,7 @@ class GluRoutedExperts(Part):
         T = x.shape[0]
         _, _, plan = be.route(be.linear_f32(x, self.w_router, tag="router"), self.top, renorm=self.renorm, score=self.score,
                               bias=self._bias, tile_rows=be.expert_tile_rows(x, self._gate_up, self._down, T * self.top))
-        act = be.experts_glu_up(x, self._gate_up, plan, self.act, self.limit, self.alpha)
+        act = be.experts_glu_up(x, self._gate_up, plan, self.act, self.limit, self.alpha, self._block)
         parts = be.experts_down(act, self._down, plan, T, self.top, scale=True)
         return Summands(parts, None if self.shared is None else self.shared.forward(x, ctx, None))
 

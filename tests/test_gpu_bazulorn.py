@@ -150,6 +150,39 @@ def test_router_softmax_over_the_chosen_logits(E, top):
     assert not torch.equal(idx0, idx)                      # the bias does change the choice
 
 
+@pytest.mark.parametrize("F,T", [(64, 700), (48, 700), (40, 700), (40, 90), (32, 90)])
+def test_clamped_experts_long_and_short_row_lists(F, T):
+    """1,400 (token, expert) rows take the tcgen05 grouped products: with an inner size in steps of 16 the gate/up
+    product activates in its epilogue on weights kept in blocks of 16 + 16 rows; other inner sizes and short row
+    lists activate in a pass of their own, on either layout. A small limit, so that the clamps bite."""
+    from rllm_b200.parts import GluRoutedExperts
+    W, E, top, limit = 64, 5, 2, 0.6
+    w = {"x.router": rnd(E, W, seed=1, scale=0.5), "x.router.b": rnd(E, seed=2, scale=0.5)}
+    for e in range(E):
+        w[f"x.e{e}.gate"], w[f"x.e{e}.up"], w[f"x.e{e}.down"] = (rnd(F, W, seed=10 + e, scale=0.3), rnd(F, W, seed=40 + e, scale=0.3),
+                                                              rnd(W, F, seed=70 + e, scale=0.3))
+    ffn = GluRoutedExperts(W, F, E, top, act="swish_clamped", limit=limit, alpha=P.SWISH_ALPHA, router_bias=True)
+    bind(ffn, w, "bfloat16", "x.")
+    x = rnd(T, W, seed=3).bfloat16()
+    mlp = {"kind": "moe", "expert": {"ff": F, "limit": limit}, "router": {"experts": E, "top": top}}
+    want = P.feed_forward(x.double(), as_stored(w, "bfloat16"), "x.", mlp)
+    assert rel(P.feed_forward(x.double(), as_stored(w, "bfloat16"), "x.", dict(mlp, expert={"ff": F, "limit": 9.0})), want) > 1e-2
+
+    class Ctx:
+        backend = Harness("bfloat16", []).backend
+    be, seen = Ctx.backend, []
+    orig = be._mix.grouped_gemm_tc
+    be._mix.grouped_gemm_tc = lambda *a, **k: (seen.append(a[4]), orig(*a, **k))[1]
+    try:
+        out = ffn.forward(x.to(DEV), Ctx)
+    finally:
+        be._mix.grouped_gemm_tc = orig
+    if seen:          # the down product joins where its inner size allows
+        assert seen[0] == (be._mix.GEPI_SILU_GATED if F % 16 == 0 else be._mix.GEPI_STORE_F32)
+    assert (F, T) != (64, 700) or seen == [be._mix.GEPI_SILU_GATED, be._mix.GEPI_STORE_F32]
+    assert rel(out.parts.sum(1), want) < 2e-2
+
+
 @pytest.mark.parametrize("taps", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("dtype", list(DT))
 def test_short_convolution_over_portions(dtype, taps):
