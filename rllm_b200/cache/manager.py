@@ -3,9 +3,10 @@ group of layers with equal needs, and slots of fixed-size per-request state.
 
 How a layer's need is served is looked up by the class of its spec (`parts.base.CacheKind`,
 `register_cache_kind`); the manager knows no spec class by name. Layers of a paged kind are
-grouped by equal specs (`KVCacheSpec`: kv heads, head sizes, window, block rule). Each group has pages of its
+grouped by equal specs (`KVCacheSpec`: kv heads, head sizes, window, block rule, kept first positions). Each group has pages of its
 own, and a pool of its own size: a group that keeps every key grows with the request, a group
-with a window gives pages back as soon as the window has passed them, and the pages of a request
+with a window gives pages back as soon as the window has passed them (but never the pages of the first positions
+that its queries keep seeing), and the pages of a request
 that ends return at once and are handed out again. Layers of a slot kind (`StateSpec`) get one
 slot per live request from a slot pool, zeroed when the request opens; Llama has none, the pool
 then has no tensors.
@@ -145,6 +146,9 @@ class CacheManager:
             chunk = cache_kind_of(gs).chunk(gs)
             if chunk is not None and self._L.cache_set_chunk(self._ptr, gi, int(chunk)):
                 raise ValueError(f"cache group {gi}: a block rule of {chunk} positions was refused")
+            kept = cache_kind_of(gs).keep_first(gs)
+            if kept and self._L.cache_set_keep_first(self._ptr, gi, int(kept)):
+                raise ValueError(f"cache group {gi}: {kept} kept first positions were refused")
         self.holders = Holders()
         for gi, (gs, layers) in enumerate(zip(group_specs, group_layers)):
             pool = PagePool(pages_of[gi], _ptr=self._L.cache_pool(self._ptr, gi), _holders=self.holders, _owner=self)
@@ -198,7 +202,8 @@ class CacheManager:
         return rc
 
     def first_needed_page(self, group: CacheGroup, num_tokens: int) -> int:
-        """Pages below this index hold only keys that no later query can see."""
+        """Pages below this index (and past those of the kept first positions, if the group has any) hold only keys
+        that no later query can see."""
         kind = cache_kind_of(group.spec)
         window, chunk = kind.window(group.spec), kind.chunk(group.spec)
         first_key = 0 if window is None else num_tokens - window + 1   # oldest key the next query sees

@@ -12,7 +12,7 @@ _SIGS = {
     "rllm_pool_release": (_I, [_P, _I, _LL]), "rllm_pool_holder": (_LL, [_P, _I]), "rllm_pool_nobody": (_LL, []),
     "rllm_pool_num_free": (_I, [_P]), "rllm_pool_num_pages": (_I, [_P]), "rllm_pool_check": (_I, [_P]),
     "rllm_cache_new": (_P, [_I, POINTER(_I), POINTER(_I), _I, _I]), "rllm_cache_delete": (None, [_P]),
-    "rllm_cache_set_chunk": (_I, [_P, _I, _I]),
+    "rllm_cache_set_chunk": (_I, [_P, _I, _I]), "rllm_cache_set_keep_first": (_I, [_P, _I, _I]),
     "rllm_cache_pool": (_P, [_P, _I]), "rllm_cache_slots": (_P, [_P]), "rllm_cache_open": (_I, [_P, _LL]),
     "rllm_cache_reserve": (_I, [_P, _I, _I]), "rllm_cache_can_reserve": (_I, [_P, _I, _I]),
     "rllm_cache_commit": (_I, [_P, _I, _I]), "rllm_cache_trim": (_I, [_P, _I]), "rllm_cache_close": (_I, [_P, _I]),

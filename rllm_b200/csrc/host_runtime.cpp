@@ -75,12 +75,13 @@ struct Cache {
   std::vector<Pool> pools;           // per group
   std::vector<int> window;           // per group, < 0: every key is kept
   std::vector<int> chunk;            // per group, > 0: a query sees only its own block of this many positions
+  std::vector<int> keep_first;       // per group: positions below this number stay visible whatever the window says
   Pool slots;
   std::vector<Holding> held;         // by state slot
   long long serials = 0;
   Cache(int G, const int* num_pages, const int* windows, int ps, int max_requests)
       : page_size(ps), slots(max_requests), held((size_t)max_requests) {
-    for (int g = 0; g < G; ++g) { pools.emplace_back(num_pages[g]); window.push_back(windows[g]); chunk.push_back(0); }
+    for (int g = 0; g < G; ++g) { pools.emplace_back(num_pages[g]); window.push_back(windows[g]); chunk.push_back(0); keep_first.push_back(0); }
   }
   int pages_for(int tokens) const { return (tokens + page_size - 1) / page_size; }
 };
@@ -127,6 +128,14 @@ RLLM_API int rllm_cache_set_chunk(void* cv, int group, int chunk) {
   Cache* c = static_cast<Cache*>(cv);
   if (group < 0 || group >= (int)c->pools.size() || chunk < 0) return -1;
   c->chunk[(size_t)group] = chunk;
+  return 0;
+}
+// Group `group` serves layers whose queries see the first `n` positions whatever their window says: the pages of
+// those positions are never given back while the request lives. 0: no such rule.
+RLLM_API int rllm_cache_set_keep_first(void* cv, int group, int n) {
+  Cache* c = static_cast<Cache*>(cv);
+  if (group < 0 || group >= (int)c->pools.size() || n < 0) return -1;
+  c->keep_first[(size_t)group] = n;
   return 0;
 }
 RLLM_API void* rllm_cache_pool(void* c, int group) { return &static_cast<Cache*>(c)->pools[(size_t)group]; }
@@ -195,7 +204,7 @@ RLLM_API int rllm_cache_commit(void* cv, int handle, int new_total) {
     }
     int last = first_key > 0 ? first_key / c->page_size : 0;
     if (last > (int)h->pages[g].size()) last = (int)h->pages[g].size();
-    for (int i = 0; i < last; ++i) {
+    for (int i = c->pages_for(c->keep_first[g]); i < last; ++i) {
       int& page = h->pages[g][(size_t)i];
       if (page >= 0) {
         const int rc = c->pools[g].release(page, h->rid);

@@ -5,7 +5,10 @@
 //   * a rotation of the first `rot` dimensions of a head, dimension i paired with i + rot/2, the rest passing;
 //   * a mask that is causal and, besides, a window (the last `window` positions) and/or a block rule (only
 //     the positions of the query's own block of `chunk` positions, blocks counted from position 0);
+//   * kept first keys: with `keep_first` > 0 a query also sees every position below that number, whatever the window says;
 //   * a sink: a learned number per head that joins the softmax's denominator with no key and no value;
+//   * sigmoid weights in place of the softmax (`sigmoid` != 0): a visible key's weight is
+//     sigmoid(score + bias[head]), not normalised over the keys (`sinks` then holds the biases);
 //   * an output gate: head h's output times sigmoid(gate[t, h]).
 //
 // qk_norm_rope_store prepares a step's queries (in place) and writes its keys and values into their pages;
@@ -182,7 +185,7 @@ sink_attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T*
                            const int* __restrict__ token_seq, const int* __restrict__ positions,
                            const int* __restrict__ block_table, int bt_stride, int n_tokens, int nh, int nkv, int kd,
                            int vd, int page_size, float scale, int window, int chunk, const float* __restrict__ sinks,
-                           const float* __restrict__ gate, int gate_ld) {
+                           const float* __restrict__ gate, int gate_ld, int keep_first, int sigmoid) {
   pdl_launch();
   pdl_wait();
   __shared__ float qs[WARPS][MAX_D];
@@ -205,14 +208,19 @@ sink_attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T*
   float acc[NACC];
 #pragma unroll
   for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
-  float m = sinks ? sinks[h] : -INFINITY, l = sinks ? 1.f : 0.f;
+  float m = (sinks && !sigmoid) ? sinks[h] : -INFINITY, l = (sinks && !sigmoid) ? 1.f : 0.f;
+  const float sbias = (sinks && sigmoid) ? sinks[h] : 0.f;
 
   typedef typename Vec16<T>::V V;
   constexpr int VN = Vec16<T>::N;
 
-  for (int base = start; base <= pos; base += 32) {
+  // the kept first keys that lie before the window's first key, then the window's keys
+  const int kept = min(keep_first, start);
+  for (int seg = kept > 0 ? 0 : 1; seg < 2; ++seg) {
+  const int seg_lo = seg ? start : 0, seg_hi = seg ? pos : kept - 1;
+  for (int base = seg_lo; base <= seg_hi; base += 32) {
     const int j = base + lane;
-    bool valid = j <= pos;
+    bool valid = j <= seg_hi;
     float s = -INFINITY;
     long long slot = 0;
     const int page = valid ? bt[j / page_size] : -1;
@@ -229,13 +237,18 @@ sink_attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T*
       }
       s = dsum;
     }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float p = valid ? expf(s - m_new) : 0.f;
-    const float corr = expf(m - m_new);
-    l = l * corr + warp_sum(p);
+    float p, m_new = m;
+    if (sigmoid) {
+      p = valid ? 1.f / (1.f + expf(-(s + sbias))) : 0.f;
+    } else {
+      m_new = fmaxf(m, warp_max(s));
+      p = valid ? expf(s - m_new) : 0.f;
+      const float corr = expf(m - m_new);
+      l = l * corr + warp_sum(p);
 #pragma unroll
-    for (int i = 0; i < NACC; ++i) acc[i] *= corr;
-    const int cnt = min(32, pos - base + 1);
+      for (int i = 0; i < NACC; ++i) acc[i] *= corr;
+    }
+    const int cnt = min(32, seg_hi - base + 1);
     for (int jj = 0; jj < cnt; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const long long sj = __shfl_sync(0xffffffffu, slot, jj);
@@ -248,7 +261,8 @@ sink_attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T*
     }
     m = m_new;
   }
-  float f = l > 0.f ? 1.f / l : 0.f;
+  }
+  float f = sigmoid ? 1.f : (l > 0.f ? 1.f / l : 0.f);
   if (gate) f *= 1.f / (1.f + expf(-gate[(size_t)t * gate_ld + h]));
   T* op = out + (size_t)t * out_stride + (size_t)h * vd;
 #pragma unroll
@@ -313,15 +327,15 @@ RLLM_API int rllm_qk_norm_rope_store(int dt, void* proj, long long ld, int q_off
   return ERR_BAD_DTYPE;
 }
 
-// q [T, ...] row stride q_stride, head h at h * kd; out [T, ...] head h at h * vd. sinks: float [nh] or null;
-// gate: float logits [T, gate_ld] or null. window, chunk: 0 = none.
+// q [T, ...] row stride q_stride, head h at h * kd; out [T, ...] head h at h * vd. sinks: float [nh] or null (with
+// `sigmoid` the biases of the sigmoid weights); gate: float logits [T, gate_ld] or null. window, chunk, keep_first: 0 = none.
 RLLM_API int rllm_sink_attention_simt(int dt, const void* q, long long q_stride, const void* kcache, const void* vcache,
                                       void* out, long long out_stride, const int* token_seq, const int* positions,
                                       const int* block_table, int bt_stride, int n_tokens, int nh, int nkv, int kd, int vd,
                                       int page_size, float scale, int window, int chunk, const float* sinks,
-                                      const float* gate, int gate_ld, void* stream) {
+                                      const float* gate, int gate_ld, int keep_first, int sigmoid, void* stream) {
   if (n_tokens <= 0) return 0;
-  if (kd <= 0 || kd > MAX_D || vd <= 0 || vd > MAX_D || nkv <= 0 || nh % nkv || page_size <= 0)
+  if (kd <= 0 || kd > MAX_D || vd <= 0 || vd > MAX_D || nkv <= 0 || nh % nkv || page_size <= 0 || keep_first < 0)
     return ERR_BAD_SIZE;
   const long long warps = (long long)n_tokens * nh;
   const long long blocks = (warps + WARPS - 1) / WARPS;
@@ -331,11 +345,11 @@ RLLM_API int rllm_sink_attention_simt(int dt, const void* q, long long q_stride,
     return launch_ex(sink_attention_simt_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, s, 1, (const float*)q,
                      q_stride, (const float*)kcache, (const float*)vcache, (float*)out, out_stride, token_seq, positions,
                      block_table, bt_stride, n_tokens, nh, nkv, kd, vd, page_size, scale, window, chunk, sinks, gate,
-                     gate_ld);
+                     gate_ld, keep_first, sigmoid);
   if (dt == DT_BF16)
     return launch_ex(sink_attention_simt_kernel<bf16>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, s, 1, (const bf16*)q,
                      q_stride, (const bf16*)kcache, (const bf16*)vcache, (bf16*)out, out_stride, token_seq, positions,
                      block_table, bt_stride, n_tokens, nh, nkv, kd, vd, page_size, scale, window, chunk, sinks, gate,
-                     gate_ld);
+                     gate_ld, keep_first, sigmoid);
   return ERR_BAD_DTYPE;
 }

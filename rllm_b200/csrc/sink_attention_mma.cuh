@@ -8,8 +8,10 @@
 // what the host cannot know when a decode graph is captured. Keys come in tiles of 64, aligned to 64 from
 // position 0, copied through the block table by `cp.async` (16 bytes a copy, one tile in flight beside the one at work); only the
 // tiles between the first key any row sees (window and block rule) and the last row's own position are
-// walked, keys outside a row's mask get -inf. The sink opens a row's running softmax as a key of score `sink`
-// and value zero. With `splits` > 1 the CTAs of grid.z share a tile's key tiles in fixed ranges and write
+// walked (with kept first keys: the tiles of those keys first, then the window's), keys outside a row's mask get
+// -inf. The sink opens a row's running softmax as a key of score `sink` and value zero. SIG: a visible key's weight
+// is sigmoid(score + bias[head]) and nothing is normalised; the running maximum then stays 0 and the denominator 1,
+// so that the joins of parts below are plain sums. With `splits` > 1 the CTAs of grid.z share a tile's key tiles in fixed ranges and write
 // unnormalised parts (sum, maximum, denominator) that sink_attention_merge joins in range order; the sink goes
 // with the first range, the output gate with whoever writes the result. Head sizes are padded with zeros in
 // shared memory to DP (64 or 128) numbers. Steps whose sequences bring at most 16 rows each (decoding) take the
@@ -64,6 +66,7 @@ struct Args {
   const float* sinks; const float* gate; int gate_ld;
   int splits; float* pacc; float* pml;
   int page_shift;              // log2(page_size), or -1 when it is no power of two
+  int keep_first;              // positions below this number are seen whatever the window says
 };
 
 __device__ __forceinline__ int first_key(int pos, int window, int chunk) {
@@ -75,7 +78,7 @@ __device__ __forceinline__ int first_key(int pos, int window, int chunk) {
 // FEW: the step's sequences bring at most 16 rows each (single tokens with up to 16 heads a kv head). The four warps
 // then all hold the tile's 16 rows and split each tile's 64 keys between them (16 keys a warp), each with a running
 // softmax of its own; the four are joined in warp order through shared memory at the end.
-template <int DP, bool FEW>
+template <int DP, bool FEW, bool SIG>
 __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args p) {
   pdl_launch();
   pdl_wait();
@@ -118,12 +121,17 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
   const int tok_lo = row_base / Gq, tok_hi = min(ql - 1, (row_base + ROWS - 1) / Gq);
   const int pos_lo = p.positions[q0 + tok_lo], pos_hi = p.positions[q0 + tok_hi];
   const int key_lo = first_key(pos_lo, p.window, p.chunk);
-  int tile0 = key_lo / KEYS, tile1 = pos_hi / KEYS + 1;           // key tiles [tile0, tile1)
+  // key tiles: those of the kept first keys that the window's walk does not reach, [0, n_kept), then the window's,
+  // [win0, pos_hi / KEYS]; walked as one list of `n1 - n0` entries
+  const int win0 = key_lo / KEYS;
+  const int n_kept = min((min(p.keep_first, key_lo) + KEYS - 1) / KEYS, win0);
+  int n0 = 0, n1 = n_kept + pos_hi / KEYS + 1 - win0;
   if (p.splits > 1) {
-    const int per = (tile1 - tile0 + p.splits - 1) / p.splits;
-    tile0 += z * per;
-    tile1 = min(tile1, tile0 + per);
+    const int per = (n1 + p.splits - 1) / p.splits;
+    n0 = z * per;
+    n1 = min(n1, n0 + per);
   }
+  auto tile_of = [&](int n) { return n < n_kept ? n : win0 + (n - n_kept); };
   const int* bt = p.block_table + (size_t)s * p.bt_stride;
 
   // zero the tiles once where a head is narrower than DP: the columns beyond kd / vd are never copied into
@@ -139,7 +147,7 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
   const int lk = tid >> 1, lh = tid & 1;
   auto load_tile = [&](int tile, int stage) {
     const int j = tile * KEYS + lk;
-    bool ok = j >= key_lo && j <= pos_hi;
+    bool ok = (j >= key_lo || j < p.keep_first) && j <= pos_hi;
     const int pi = p.page_shift >= 0 ? j >> p.page_shift : j / p.page_size;
     const int page = ok ? bt[pi] : -1;
     ok = ok && page >= 0;
@@ -180,20 +188,30 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
   float o[DP / 8][4];
 #pragma unroll
   for (int i = 0; i < DP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  const bool with_sink = p.sinks && z == 0 && (!FEW || warp == 0);
-  float m0 = (with_sink && v0) ? p.sinks[h0] * 1.4426950408889634f : -INFINITY, l0 = (with_sink && v0) ? 1.f : 0.f;
-  float m1 = (with_sink && v1) ? p.sinks[h1] * 1.4426950408889634f : -INFINITY, l1 = (with_sink && v1) ? 1.f : 0.f;
+  const bool first_part = z == 0 && (!FEW || warp == 0);      // the part that opens the softmax (SIG: that owns the 1)
+  const bool with_sink = !SIG && p.sinks && first_part;
+  float m0 = (with_sink && v0) ? p.sinks[h0] * 1.4426950408889634f : -INFINITY;
+  float m1 = (with_sink && v1) ? p.sinks[h1] * 1.4426950408889634f : -INFINITY;
+  float l0 = ((with_sink || (SIG && first_part)) && v0) ? 1.f : 0.f, l1 = ((with_sink || (SIG && first_part)) && v1) ? 1.f : 0.f;
+  float sb0 = 0.f, sb1 = 0.f;                       // SIG: the heads' biases in the log2 domain
+  if (SIG) {
+    sb0 = (p.sinks && v0) ? p.sinks[h0] * 1.4426950408889634f : 0.f;
+    sb1 = (p.sinks && v1) ? p.sinks[h1] * 1.4426950408889634f : 0.f;
+    m0 = v0 ? 0.f : -INFINITY;
+    m1 = v1 ? 0.f : -INFINITY;
+  }
 
   // STAGES - 1 tiles are on their way while one is worked on (a commit per tile, empty past the end, so that
   // the count of groups in flight says which tile has landed)
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {
-    if (tile0 + i < tile1) load_tile(tile0 + i, i);
+    if (n0 + i < n1) load_tile(tile_of(n0 + i), i);
     cp_async_commit();
   }
-  for (int tile = tile0; tile < tile1; ++tile) {
-    const int stage = (tile - tile0) % STAGES;
-    if (tile + STAGES - 1 < tile1) load_tile(tile + STAGES - 1, (tile - tile0 + STAGES - 1) % STAGES);
+  for (int n = n0; n < n1; ++n) {
+    const int tile = tile_of(n);
+    const int stage = (n - n0) % STAGES;
+    if (n + STAGES - 1 < n1) load_tile(tile_of(n + STAGES - 1), (n - n0 + STAGES - 1) % STAGES);
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
     __syncthreads();
@@ -220,15 +238,16 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
     // mask (only where a row's edge crosses the tile), scale into the log2 domain, running maximum
     const int key0 = tile * KEYS + kofs;
     float mx0 = -INFINITY, mx1 = -INFINITY;
-    const bool edge = !v0 || !v1 || key0 < max(st0, st1) || key0 + NT * 8 - 1 > min(pos0, pos1);
+    const bool edge = !v0 || !v1 || (key0 < max(st0, st1) && key0 + NT * 8 > p.keep_first) ||
+                      key0 + NT * 8 - 1 > min(pos0, pos1);
     if (__any_sync(0xffffffffu, edge)) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int j = key0 + nt * 8 + (lane & 3) * 2 + e;
-          const float a = (v0 && j >= st0 && j <= pos0) ? sc[nt][e] * p.scale_log2 : -INFINITY;
-          const float c = (v1 && j >= st1 && j <= pos1) ? sc[nt][2 + e] * p.scale_log2 : -INFINITY;
+          const float a = (v0 && (j >= st0 || j < p.keep_first) && j <= pos0) ? sc[nt][e] * p.scale_log2 : -INFINITY;
+          const float c = (v1 && (j >= st1 || j < p.keep_first) && j <= pos1) ? sc[nt][2 + e] * p.scale_log2 : -INFINITY;
           sc[nt][e] = a; sc[nt][2 + e] = c;
           mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, c);
         }
@@ -241,12 +260,20 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
         mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1])); mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
       }
     }
+    if (SIG) {
+      // sigmoid(x) = 1 / (1 + 2^(-x log2 e)); a masked key's -inf gives 1 / (1 + inf) = 0
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        sc[nt][0] = __frcp_rn(1.f + fast_exp2(-(sc[nt][0] + sb0))); sc[nt][1] = __frcp_rn(1.f + fast_exp2(-(sc[nt][1] + sb0)));
+        sc[nt][2] = __frcp_rn(1.f + fast_exp2(-(sc[nt][2] + sb1))); sc[nt][3] = __frcp_rn(1.f + fast_exp2(-(sc[nt][3] + sb1)));
+      }
+    } else {
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-    const float u0 = n0 == -INFINITY ? 0.f : n0, u1 = n1 == -INFINITY ? 0.f : n1;     // a row that has seen nothing yet
+    const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);
+    const float u0 = nm0 == -INFINITY ? 0.f : nm0, u1 = nm1 == -INFINITY ? 0.f : nm1;     // a row that has seen nothing yet
     const float c0 = fast_exp2(m0 - u0), c1 = fast_exp2(m1 - u1);
-    m0 = n0; m1 = n1;
+    m0 = nm0; m1 = nm1;
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -259,6 +286,7 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
     l0 = l0 * c0 + s0; l1 = l1 * c1 + s1;
 #pragma unroll
     for (int i = 0; i < DP / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+    }
     // O += P V
 #pragma unroll
     for (int kk = 0; kk < NT / 2; ++kk) {
@@ -404,10 +432,12 @@ RLLM_API int rllm_sink_attention_mma(const void* q, long long q_stride, const vo
                                      long long out_stride, const int* positions, const int* cu_q, const int* block_table,
                                      int bt_stride, int num_seqs, int n_tokens, int max_q_len, int nh, int nkv, int kd, int vd,
                                      int page_size, float scale, int window, int chunk, const float* sinks, const float* gate,
-                                     int gate_ld, int splits, float* pacc, float* pml, void* stream) {
+                                     int gate_ld, int splits, float* pacc, float* pml, int keep_first, int sigmoid,
+                                     void* stream) {
   using namespace sinkmma;
   if (n_tokens <= 0 || num_seqs <= 0) return 0;
-  if (!rllm_sink_attention_mma_supported(DT_BF16, kd, vd, page_size) || nkv <= 0 || nh % nkv || splits < 1 || splits > 64)
+  if (!rllm_sink_attention_mma_supported(DT_BF16, kd, vd, page_size) || nkv <= 0 || nh % nkv || splits < 1 || splits > 64 ||
+      keep_first < 0)
     return ERR_BAD_SIZE;
   if (q_stride % 2 || out_stride % 2 || (splits > 1 && (!pacc || !pml))) return ERR_BAD_ALIGN;
   const int Gq = nh / nkv;
@@ -415,7 +445,7 @@ RLLM_API int rllm_sink_attention_mma(const void* q, long long q_stride, const vo
   if (tiles > 2147483647LL || nkv > 65535) return ERR_TOO_LARGE;
   Args a = {(const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, (bf16*)out, out_stride, positions, cu_q,
             block_table, bt_stride, num_seqs, nh, nkv, kd, vd, page_size, scale * 1.4426950408889634f, window, chunk, sinks,
-            gate, gate_ld, splits, pacc, pml, -1};
+            gate, gate_ld, splits, pacc, pml, -1, keep_first};
   for (int sft = 0; sft < 31; ++sft) if ((1 << sft) == page_size) a.page_shift = sft;
   cudaStream_t s = (cudaStream_t)stream;
   const dim3 grid((unsigned)tiles, (unsigned)nkv, (unsigned)splits);
@@ -423,14 +453,16 @@ RLLM_API int rllm_sink_attention_mma(const void* q, long long q_stride, const vo
   const int smem = 2 * STAGES * KEYS * (dp + 8) * (int)sizeof(bf16);     // also holds the FEW join: 4 x 16 x (dp + 2) floats
   const bool few = (long long)max_q_len * Gq <= 16;             // every sequence's rows fit one warp's 16
   int rc;
-#define GO(D, F)                                                                                     \
-  {                                                                                                  \
-    static bool done[64] = {};                                                                       \
-    if ((rc = allow_dynamic_smem(sink_attention_mma_kernel<D, F>, smem, done))) return rc;           \
-    rc = launch_ex(sink_attention_mma_kernel<D, F>, grid, dim3(THREADS), (size_t)smem, s, 1, a);     \
+#define GO(D, F, G)                                                                                     \
+  {                                                                                                     \
+    static bool done[64] = {};                                                                          \
+    if ((rc = allow_dynamic_smem(sink_attention_mma_kernel<D, F, G>, smem, done))) return rc;           \
+    rc = launch_ex(sink_attention_mma_kernel<D, F, G>, grid, dim3(THREADS), (size_t)smem, s, 1, a);     \
   }
-  if (dp == 64) { if (few) GO(64, true) else GO(64, false) }
-  else { if (few) GO(128, true) else GO(128, false) }
+#define GO2(D, F) { if (sigmoid) GO(D, F, true) else GO(D, F, false) }
+  if (dp == 64) { if (few) GO2(64, true) else GO2(64, false) }
+  else { if (few) GO2(128, true) else GO2(128, false) }
+#undef GO2
 #undef GO
   if (rc || splits == 1) return rc;
   const long long rows = (long long)n_tokens * nh;

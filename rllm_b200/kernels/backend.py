@@ -277,7 +277,10 @@ class Backend:
         return h if copy is None else copy
 
     def linear_act(self, x, w, act):
-        """act(x W^T) in the run dtype; act "relu2" = max(., 0)^2."""
+        """act(x W^T) in the run dtype; act "relu2" = max(., 0)^2, "gelu_tanh" = gelu in its tanh form (on the float
+        product, rounded once)."""
+        if act == "gelu_tanh":
+            return self._hy.act_rows(self.linear_f32(x, w, tag="up"), self.dtype, act)
         if act != "relu2":
             raise ops.KernelError(f"activation {act!r} has no kernel")
         x = x.tensor() if isinstance(x, Normed) else x
@@ -293,21 +296,22 @@ class Backend:
                                       cache.slots if writes else None, cache.k if writes else None,
                                       cache.v if writes else None)
 
-    def sink_attention(self, q, cache, ctx, nh, scale, window, chunk, sinks, gate):
+    def sink_attention(self, q, cache, ctx, nh, scale, window, chunk, sinks, gate, keep_first=0, sigmoid=False):
         """Attention with a window and/or block mask, a sink and an output gate over pages whose keys and values
         may differ in size: bfloat16 on the tensor cores where the kernel takes the sizes, else (and in the
-        32-bit run) in float on the CUDA cores."""
+        32-bit run) in float on the CUDA cores. `keep_first`: positions below it are seen whatever the window says.
+        `sigmoid`: no softmax, a visible key's weight is sigmoid(score + sinks[head])."""
         sk = self._sink
         kd, vd, nkv = cache.k.shape[3], cache.v.shape[3], cache.k.shape[1]
         tc = self.fast and os.environ.get("RLLM_B200_NO_TC_ATTENTION") != "1"
         # keys a query of this step can see at most, known without a device read (graph captures included)
         keys = ctx.max_kv_len
         if window:
-            keys = min(keys, window + ctx.max_q_len)
+            keys = min(keys, window + ctx.max_q_len + keep_first)
         if chunk:
             keys = min(keys, chunk)
         G = nh // nkv
-        if tc and kd == vd and self._sm100.attention_supported(q, cache.k):
+        if tc and kd == vd and not keep_first and not sigmoid and self._sm100.attention_supported(q, cache.k):
             # equal head sizes of 64 or 128: the kernels of plain grouped-query attention take the mask, the sink
             # and the gate as well (the clusters of the decode kernel, tcgen05 for long portions)
             sm = self._sm100
@@ -327,9 +331,10 @@ class Backend:
             # ranges of keys per row tile: up to four CTAs an SM are resident, a range is at least 128 keys
             splits = max(1, min(16, 4 * self.sm_count // max(tiles, 1), keys // 128))
             return sk.sink_attention_mma(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, ctx.cu_q,
-                                         ctx.num_seqs, ctx.max_q_len, nh, scale, window, chunk, sinks, gate, splits, keys)
+                                         ctx.num_seqs, ctx.max_q_len, nh, scale, window, chunk, sinks, gate, splits, keys,
+                                         keep_first, sigmoid)
         return sk.sink_attention_simt(q, cache.k, cache.v, ctx.token_seq, ctx.positions, cache.block_table, nh, scale,
-                                      window, chunk, sinks, gate)
+                                      window, chunk, sinks, gate, keep_first, sigmoid)
 
     def latent_prepare(self, *a, **k):
         return self._mix.latent_prepare(*a, **k)
@@ -420,6 +425,20 @@ class Backend:
 
     def add_bias_f32(self, y, bias):
         return self._hy.add_bias_f32(y, bias)
+
+    def gated_add(self, h, gate, bias, y):
+        """h += sigmoid(gate + bias) * y, in float and in one pass; y a float tensor [T, H] or `ScaledSum` (one or two
+        float tensors with a coefficient each)."""
+        terms = list(y.terms) if hasattr(y, "terms") else [(y, 1.0)]
+        return self._hy.gated_add(h, gate, bias, terms)
+
+    def mix_values(self, proj, v_off, n_cols, first, lam):
+        """The value columns of `proj` become (1 - lam) v + lam first, with `first` the rows another layer kept."""
+        return self._hy.lerp_cols(proj[:, v_off: v_off + n_cols], first, n_cols, lam)
+
+    def mingru_scan(self, proj, z_off, x_off, g_off, width, bias_z, bias_x, ctx, state):
+        return self._hy.mingru_scan(proj, z_off, x_off, g_off, width, bias_z, bias_x, ctx.cu_q, ctx.num_seqs,
+                                    ctx.state_slots, state, self.dtype, ctx.max_q_len)
 
     def short_conv(self, x, col0, channels, w, bias, ctx, tail, silu=True):
         return self._hy.short_conv(x, col0, channels, w, bias, ctx.token_seq, ctx.positions, ctx.cu_q, ctx.num_seqs,

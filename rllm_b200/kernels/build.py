@@ -30,15 +30,15 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 # (grouped products, routing, the norm after a sublayer), "sink" grouped-query attention with query/key norm,
 # sink, output gate and block mask plus the row-wise work of layers that norm after the sum; all in both
 # precisions, each built only when a model uses it; "hybrid" recurrent mixers with a short convolution (a state-space
-# and a delta-rule recurrence), attention whose heads' weights are mixed, and the row-wise work of layers whose
-# sublayers run side by side.
+# and a delta-rule recurrence, a gated recurrence whose gates read only the current token), attention whose heads'
+# weights are mixed, and the row-wise work of layers whose sublayers run side by side or are gated into the stream.
 LIBRARIES: dict[str, list[str]] = {
     "simt": ["simt_basic.cu", "simt_gemm.cu", "simt_attention.cu", "sampling.cu"],
     "sm100": ["tc_gemm.cu", "stream_gemm.cu", "attn_fa.cu", "attn_decode.cu", "attn_prefill_tc.cu", "wait_probe.cu"],
     "mix": ["latent_attention.cu", "gla.cu"],
     "experts": ["grouped_gemm.cu", "grouped_gemm_tc.cu", "moe_route.cu"],
     "sink": ["sink_attention.cu", "stream_ops.cu"],
-    "hybrid": ["recurrent.cu", "talk_attention.cu", "row_mix.cu"],
+    "hybrid": ["recurrent.cu", "talk_attention.cu", "row_mix.cu", "gated_ops.cu"],
     "host": ["host_runtime.cpp"],          # no CUDA: the cache manager's bookkeeping and metadata writer
 }
 

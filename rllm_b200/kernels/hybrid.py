@@ -32,6 +32,11 @@ ops.register_signatures("hybrid", {
     "rllm_talk_attention_simt": [c_int, _P, _LL, _P, _P, _P, _P, _P, _LL, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_int, c_int, _P],
     "rllm_talk_attention_mma_supported": [c_int, c_int, c_int, c_int, c_int],
+    "rllm_gated_add": [_P, _P, _LL, _P, _P, c_float, _P, c_float, c_int, c_int, _P],
+    "rllm_act_rows": [_P, c_int, _LL, _P, c_int, c_int, c_int, c_int, _P],
+    "rllm_lerp_cols": [c_int, _P, _LL, _P, _LL, c_int, c_int, _P, _P],
+    "rllm_mingru_scan": [_P, _LL, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P,
+                         _P, _P],
     "rllm_talk_attention_mma": [_P, _LL, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_float, c_int, c_int, _P, _P, _P],
 })
@@ -144,7 +149,95 @@ def add_bias_f32(y, bias) -> torch.Tensor:
     return y
 
 
+ROW_ACTS = {"gelu_tanh": 0}
+
+
+def act_rows(x, out_dtype, act: str) -> torch.Tensor:
+    """act(x) element by element for x [R, F] (float32 or the run's type; unit inner stride) -> [R, F] of `out_dtype`;
+    the activation runs in float and is rounded once. "gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))."""
+    if act not in ROW_ACTS:
+        raise KernelError(f"activation {act!r} has no kernel (known: {sorted(ROW_ACTS)})")
+    _rows(x, "x", 1)
+    R, F = x.shape
+    out = torch.empty((R, F), dtype=out_dtype, device=x.device)
+    _check(_fn("hybrid", "rllm_act_rows")(x.data_ptr(), _dt(x, "x"), x.stride(0), out.data_ptr(), _dt(out, "out"), R, F,
+                                          ROW_ACTS[act], _stream()), "act_rows")
+    return out
+
+
+def gated_add(h, gate, bias, terms) -> torch.Tensor:
+    """h (float32 [T, W], in place) += sigmoid(gate + bias) * sum_i c_i * y_i, element by element. `gate` float32
+    [T, >= W] logits (unit inner stride), `bias` float32 [W] or None, `terms` one or two (y_i float32 [T, W], c_i)."""
+    _f32(h, "h")
+    T, W = h.shape
+    _rows(gate, "gate", W)
+    if gate.dtype != torch.float32 or gate.shape[0] != T:
+        raise KernelError("the gate's logits must be float32 rows, one per token")
+    if bias is not None:
+        _f32(bias, "gate bias", (W,))
+    if not 1 <= len(terms) <= 2:
+        raise KernelError("gated_add takes one or two summands")
+    for y, _ in terms:
+        _f32(y, "summand", (T, W))
+    (y0, c0), (y1, c1) = terms[0], (terms[1] if len(terms) == 2 else (None, 0.0))
+    _check(_fn("hybrid", "rllm_gated_add")(h.data_ptr(), gate.data_ptr(), gate.stride(0), _ptr(bias), y0.data_ptr(), float(c0),
+                                           _ptr(y1), float(c1), T, W, _stream()), "gated_add")
+    return h
+
+
+def lerp_cols(dst, src, n_cols, lam) -> torch.Tensor:
+    """dst[:, :n_cols] <- (1 - lam) dst[:, :n_cols] + lam src[:, :n_cols] in place, in float, rounded once. dst and src
+    rows of one type with unit inner stride (views with longer row strides are fine); `lam` one float32 on the device."""
+    _rows(dst, "dst", n_cols)
+    _rows(src, "src", n_cols)
+    if dst.dtype != src.dtype or dst.shape[0] != src.shape[0]:
+        raise KernelError("lerp_cols takes two sets of rows of one type and count")
+    _f32(lam, "lam")
+    if lam.numel() != 1:
+        raise KernelError("lerp_cols takes one coefficient")
+    _check(_fn("hybrid", "rllm_lerp_cols")(_dt(dst, "dst"), dst.data_ptr(), dst.stride(0), src.data_ptr(), src.stride(0),
+                                           dst.shape[0], int(n_cols), lam.data_ptr(), _stream()), "lerp_cols")
+    return dst
+
+
 # --------------------------------------------------------------------------- recurrent mixers
+
+MINGRU_CHUNK = 32          # tokens a piece of a long portion has; portions of up to twice that run as one piece
+
+
+def mingru_scan(proj, z_off, x_off, g_off, width, bias_z, bias_x, cu_q, num_seqs, state_slots, state, out_dtype,
+                max_q_len: int, chunk: int | None = None) -> torch.Tensor:
+    """See csrc/gated_ops.cu. proj float32 [T, cols] with the update gate's, the candidate's and the output gate's
+    logits at z_off, x_off, g_off (`width` columns each); biases float32 [width] or None; `state` float32 [slots, width]
+    is updated. -> [T, width] of `out_dtype`: S_t * silu(g_t). Portions longer than two chunks are cut into pieces that
+    run side by side (`chunk` None: MINGRU_CHUNK; 0: never)."""
+    _rows(proj, "proj", max(z_off, x_off, g_off) + width)
+    if proj.dtype != torch.float32:
+        raise KernelError("mingru_scan takes float32 projections")
+    T = proj.shape[0]
+    for b, n in ((bias_z, "update bias"), (bias_x, "candidate bias")):
+        if b is not None:
+            _f32(b, n, (width,))
+    _i32(cu_q, "cu_q", num_seqs + 1)
+    if state_slots is not None:
+        _i32(state_slots, "state_slots", num_seqs)
+        _f32(state, "state")
+        if state.dim() != 2 or state.shape[1] != width:
+            raise KernelError(f"state must be [slots, {width}], got {list(state.shape)}")
+    chunk = MINGRU_CHUNK if chunk is None else int(chunk)
+    if max_q_len <= 2 * chunk:
+        chunk = 0
+    ca = cb = s0 = None
+    if chunk > 0:
+        ca = torch.empty((T // chunk + num_seqs, width), dtype=torch.float32, device=proj.device)
+        cb = torch.empty_like(ca)
+        s0 = torch.empty((num_seqs, width), dtype=torch.float32, device=proj.device)
+    out = torch.empty((T, width), dtype=out_dtype, device=proj.device)
+    _check(_fn("hybrid", "rllm_mingru_scan")(
+        proj.data_ptr(), proj.stride(0), int(z_off), int(x_off), int(g_off), _ptr(bias_z), _ptr(bias_x), cu_q.data_ptr(),
+        _ptr(state_slots), _ptr(state) if state_slots is not None else None, out.data_ptr(), _dt(out, "out"), T, int(num_seqs),
+        int(width), chunk, _ptr(ca), _ptr(cb), _ptr(s0), _stream()), "mingru_scan", 2 if chunk > 0 else 1)
+    return out
 
 def short_conv(x, col0, channels, w, bias, token_seq, positions, cu_q, num_seqs, state_slots, tail, silu=True) -> torch.Tensor:
     """Causal convolution over time per channel of columns [col0, col0 + channels) of x [T, cols]: float32

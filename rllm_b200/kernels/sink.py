@@ -19,10 +19,10 @@ ops.register_signatures("sink", {
     "rllm_qk_norm_rope_store": [c_int, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P,
                                 c_float, _P, _P, _P, _P, c_int, _P],
     "rllm_sink_attention_simt": [c_int, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_int, c_float, c_int, c_int, _P, _P, c_int, _P],
+                                 c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, c_int, _P],
     "rllm_sink_attention_mma_supported": [c_int, c_int, c_int, c_int],
     "rllm_sink_attention_mma": [_P, _LL, _P, _P, _P, _LL, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                c_int, c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, _P, _P, _P],
+                                c_int, c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, _P, _P, c_int, c_int, _P],
     "rllm_postnorm": [_P, _P, c_int, _P, _P, c_int, c_float, _P, c_int, c_int, c_float, _P, c_int, _P],
     "rllm_cast_rows": [_P, _P, _LL, _P],
     "rllm_gated_act": [_P, c_int, _LL, _P, c_int, c_int, c_int, c_int, _P, _P],
@@ -109,19 +109,20 @@ def _attention_args(q, kcache, vcache, token_seq, positions, block_table, nh, si
 
 
 def sink_attention_simt(q, kcache, vcache, token_seq, positions, block_table, nh, scale, window=None, chunk=None,
-                        sinks=None, gate=None) -> torch.Tensor:
+                        sinks=None, gate=None, keep_first: int = 0, sigmoid: bool = False) -> torch.Tensor:
     """Attention of every query row over its sequence's pages, in float on the CUDA cores. q [T, nh * kd] (a view
     with a longer row stride is fine); kcache [pages, nkv, page, kd]; vcache [pages, nkv, page, vd] -> [T, nh * vd]
     of q's dtype. A query at position p sees j <= p with j > p - window (if `window`) and j // chunk == p // chunk
-    (if `chunk`). `sinks` float [nh]: exp(sink) joins the denominator. `gate` float [T, >= nh]: logits of the
-    output gate."""
+    (if `chunk`), and besides every j <= p below `keep_first`. `sinks` float [nh]: exp(sink) joins the denominator.
+    `sigmoid`: no softmax, a visible key's weight is sigmoid(score + sinks[head]) (`sinks` None: no bias). `gate` float
+    [T, >= nh]: logits of the output gate."""
     T, nkv, page_size, kd, vd = _attention_args(q, kcache, vcache, token_seq, positions, block_table, nh, sinks, gate)
     out = torch.empty((T, nh * vd), dtype=q.dtype, device=q.device)
     _check(_fn("sink", "rllm_sink_attention_simt")(
         _dt(q, "q"), q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(), out.stride(0),
         token_seq.data_ptr(), positions.data_ptr(), block_table.data_ptr(), block_table.stride(0), T, nh, nkv, kd, vd,
         page_size, float(scale), int(window or 0), int(chunk or 0), _ptr(sinks), _ptr(gate),
-        0 if gate is None else gate.stride(0), _stream()), "sink_attention_simt")
+        0 if gate is None else gate.stride(0), int(keep_first or 0), int(bool(sigmoid)), _stream()), "sink_attention_simt")
     return out
 
 
@@ -131,11 +132,13 @@ def mma_supported(dtype: torch.dtype, kd: int, vd: int, page_size: int) -> bool:
 
 
 def sink_attention_mma(q, kcache, vcache, token_seq, positions, block_table, cu_q, num_seqs, max_q_len, nh, scale,
-                       window=None, chunk=None, sinks=None, gate=None, splits: int = 1, max_keys: int = 0) -> torch.Tensor:
+                       window=None, chunk=None, sinks=None, gate=None, splits: int = 1, max_keys: int = 0,
+                       keep_first: int = 0, sigmoid: bool = False) -> torch.Tensor:
     """The same attention in bfloat16 on the tensor cores (`mma.sync`, float softmax): row tiles of 64 (query,
     head-of-a-group) rows per sequence and kv head; `splits` > 1 deals a tile's keys out to that many CTAs in
     fixed ranges (steps of few rows) whose parts a second kernel merges in order. `cu_q` int32 [num_seqs + 1];
-    `max_keys`: a bound of the keys any query of the step sees (what `splits` cuts up)."""
+    `max_keys`: a bound of the keys any query of the step sees (what `splits` cuts up). `keep_first`, `sigmoid`: as in
+    `sink_attention_simt`."""
     T, nkv, page_size, kd, vd = _attention_args(q, kcache, vcache, token_seq, positions, block_table, nh, sinks, gate)
     if not mma_supported(q.dtype, kd, vd, page_size):
         raise KernelError(f"sink_attention_mma: bfloat16 with head sizes in steps of 16 up to 128, got {q.dtype} {kd}/{vd}")
@@ -150,8 +153,8 @@ def sink_attention_mma(q, kcache, vcache, token_seq, positions, block_table, cu_
         q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(), out.stride(0),
         positions.data_ptr(), cu_q.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(num_seqs), T,
         int(max_q_len), nh, nkv, kd, vd, page_size, float(scale), int(window or 0), int(chunk or 0), _ptr(sinks),
-        _ptr(gate), 0 if gate is None else gate.stride(0), splits, _ptr(pacc), _ptr(pml), _stream()),
-        "sink_attention_mma", 2 if splits > 1 else 1)
+        _ptr(gate), 0 if gate is None else gate.stride(0), splits, _ptr(pacc), _ptr(pml), int(keep_first or 0),
+        int(bool(sigmoid)), _stream()), "sink_attention_mma", 2 if splits > 1 else 1)
     return out
 
 

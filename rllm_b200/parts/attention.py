@@ -76,10 +76,18 @@ class SinkGQAttention(Part):
     * keys of `head_dim` and values of `v_dim` numbers per head;
     * `qk_norm`: queries and keys divided by their root mean square per head, times a weight of `head_dim`
       numbers shared by all heads (tensors `q.norm`, `k.norm`), before the rotation;
+      `qk_norm_weight` False: no weights, queries and keys become vectors of root mean square 1 (a plain factor
+      commutes with the rotation, so it is the same norm whether a design names it before or after the rotation);
     * `position`: a rotary part (its `rot_dim` leading dimensions of a head are rotated, the rest pass) or None;
     * the mask: causal, and a `window` (the last `window` positions) and/or a `chunk` (only the positions of the
-      query's own block of `chunk` positions, blocks counted from position 0);
+      query's own block of `chunk` positions, blocks counted from position 0); `keep_first`: the positions below
+      this number stay visible to every later query whatever the window says (their pages are never given back);
     * `sink`: one learned number per head (tensor `sink`) whose exponential joins the softmax's denominator;
+    * `weights` "sigmoid": no softmax; a visible key's weight is sigmoid(score + b_h) with one learned number per
+      head (tensor `score_bias`, None: no bias), not normalised over the keys;
+    * `value_mix`: None, or (role, key). The values of the layers that share a `key` are mixed with those of the
+      first of them: role "first" keeps its step's values for the others, role "mix" turns its own into
+      (1 - lam) v + lam v_first, lam the scalar tensor `vmix`, before they are cached;
     * `gate`: head h's output times sigmoid((W_g x)_h) (tensor `g`, one row per head), before W_o.
 
     Scores, softmax, norms, rotation and the gate's sigmoid are float. `forward(..., residual=None)` returns
@@ -90,7 +98,8 @@ class SinkGQAttention(Part):
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, v_dim: int | None = None,
                  position: Part | None = None, scale: float | None = None, window: int | None = None,
                  chunk: int | None = None, qk_norm: bool = False, sink: bool = False, gate: bool = False,
-                 eps: float = 1e-6, names=("q", "k", "v", "o")):
+                 eps: float = 1e-6, names=("q", "k", "v", "o"), qk_norm_weight: bool = True, keep_first: int = 0,
+                 weights: str = "softmax", score_bias: str | None = None, value_mix: tuple | None = None):
         if heads % kv_heads:
             raise ValueError(f"heads {heads} must be a multiple of kv_heads {kv_heads}")
         v_dim = head_dim if v_dim is None else v_dim
@@ -100,7 +109,15 @@ class SinkGQAttention(Part):
         self.position, self.window, self.chunk = position, window, chunk
         self.scale = head_dim ** -0.5 if scale is None else float(scale)
         self.qk_norm, self.sink, self.gate, self.eps, self.names = qk_norm, sink, gate, float(eps), names
-        self.w_qkv = self.w_o = self.w_g = self.q_norm = self.k_norm = self.sinks = None
+        if weights not in ("softmax", "sigmoid"):
+            raise ValueError(f"attention weights {weights!r} are not known (known: 'softmax', 'sigmoid')")
+        if weights == "sigmoid" and sink:
+            raise ValueError("a sink belongs to a softmax; sigmoid weights have none")
+        if value_mix is not None and value_mix[0] not in ("first", "mix"):
+            raise ValueError(f"value_mix role {value_mix[0]!r} is not known (known: 'first', 'mix')")
+        self.qk_norm_weight, self.keep_first, self.weights = qk_norm_weight, int(keep_first or 0), weights
+        self.score_bias, self.value_mix = score_bias, value_mix
+        self.w_qkv = self.w_o = self.w_g = self.q_norm = self.k_norm = self.sinks = self.bias = self.lam = None
 
     def children(self):
         return [] if self.position is None else [self.position]
@@ -110,22 +127,33 @@ class SinkGQAttention(Part):
         q, k, v, o = self.names
         ps = [Param("w_qkv", (Source(q, (H * D, W)), Source(k, (G * D, W)), Source(v, (G * V, W)))),
               Param("w_o", (Source(o, (W, H * V)),))]
-        if self.qk_norm:
+        if self.qk_norm and self.qk_norm_weight:
             ps += [Param("q_norm", (Source(q + ".norm", (D,), init="norm"),), role="vector"),
                    Param("k_norm", (Source(k + ".norm", (D,), init="norm"),), role="vector")]
         if self.sink:
             ps.append(Param("sinks", (Source("sink", (H,)),), role="vector"))
+        if self.weights == "sigmoid" and self.score_bias is not None:
+            ps.append(Param("bias", (Source(self.score_bias, (H,)),), role="vector"))
+        if self.value_mix is not None:
+            # the first layer of a group owns the tensor too (a checkpoint stores it), and has no use for it
+            ps.append(Param("lam", (Source("vmix", ()),), role="vector"))
         if self.gate:
             ps.append(Param("w_g", (Source("g", (H, W)),)))
         return ps
 
     def cache_spec(self):
         return KVCacheSpec(self.kv_heads, self.head_dim, self.window, self.chunk,
-                           None if self.v_dim == self.head_dim else self.v_dim)
+                           None if self.v_dim == self.head_dim else self.v_dim, self.keep_first if self.window else 0)
 
     def finalize(self, device, dtype):
+        import torch
         f32 = lambda t: None if t is None else t.float().contiguous()
         self._qn, self._kn, self._sinks = f32(self.q_norm), f32(self.k_norm), f32(self.sinks)
+        if self.qk_norm and not self.qk_norm_weight:
+            self._qn = self._kn = torch.ones(self.head_dim, dtype=torch.float32, device=device)
+        if self.weights == "sigmoid":
+            self._sinks = f32(self.bias)
+        self._lam = None if self.lam is None else self.lam.float().reshape(1).contiguous()
 
     def forward(self, x, ctx, cache, residual=None):
         be = ctx.backend
@@ -134,9 +162,19 @@ class SinkGQAttention(Part):
         proj = be.linear(x, self.w_qkv, tag="qkv")                                  # [T, q | k | v]
         gate = be.linear_f32(x, self.w_g, tag="gate") if self.gate else None         # float logits [T, H]
         pos = self.position
+        if self.value_mix is not None:
+            role, key = self.value_mix
+            if role == "first":                  # this step's values, as projected, for the layers that mix them in
+                ctx.per_forward[("value_mix", key)] = proj[:, (H + G) * D:]
+            else:
+                first = ctx.per_forward.get(("value_mix", key))
+                if first is None or first.shape[1] != G * V:
+                    raise ValueError(f"{self.prefix}: the values to mix in ({key!r}) are missing or of another size")
+                be.mix_values(proj, (H + G) * D, G * V, first, self._lam)
         be.qk_norm_rope_store(proj, 0, H * D, (H + G) * D, H, G, D, V, 0 if pos is None else pos.rot_dim,
                               self._qn, self._kn, self.eps, None if pos is None else pos.table(ctx), cache)
-        att = be.sink_attention(proj[:, : H * D], cache, ctx, H, self.scale, self.window, self.chunk, self._sinks, gate)
+        att = be.sink_attention(proj[:, : H * D], cache, ctx, H, self.scale, self.window, self.chunk, self._sinks, gate,
+                                self.keep_first if self.window else 0, self.weights == "sigmoid")
         if residual is None:
             return be.linear_f32(att, self.w_o, tag="o")
         be.linear_residual(att, self.w_o, residual)

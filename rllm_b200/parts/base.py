@@ -52,12 +52,14 @@ class KVCacheSpec:
     """Paged keys and values: `window` None keeps every key, else only the last `window`. `chunk`: a
     query sees only the keys of its own block of `chunk` positions (blocks counted from position 0), so
     the pages before the current block are given back. `v_dim`: size of a value head where it differs
-    from the key's `head_dim`."""
+    from the key's `head_dim`. `keep_first`: a query also sees the positions below this number whatever the
+    window says, so their pages are never given back."""
     kv_heads: int
     head_dim: int
     window: int | None = None
     chunk: int | None = None
     v_dim: int | None = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -105,7 +107,8 @@ class CacheKind:
     tensors by name, each with the page as its first dimension. `window(spec)` is how many positions
     a query looks back (None: all; pages that lie wholly before it go back to the pool);
     `chunk(spec)` is the size of the blocks of positions a query is confined to (None: no such rule; the
-    pages before the block of the next position go back to the pool);
+    pages before the block of the next position go back to the pool); `keep_first(spec)` how many first positions
+    stay visible whatever the window says (their pages are never given back);
     `num_pages(spec, default)` the size of the group's pool; `page_bytes(spec, page_size, dtype)`
     what one page of one layer costs (for sizing the pool from free memory).
     Kinds that are not paged get a slot per live request:
@@ -115,6 +118,7 @@ class CacheKind:
     allocate: Callable[..., dict]
     window: Callable[[Any], int | None] = lambda spec: None
     chunk: Callable[[Any], int | None] = lambda spec: None
+    keep_first: Callable[[Any], int] = lambda spec: 0
     num_pages: Callable[[Any, int], int] = lambda spec, default: default
     page_bytes: Callable[[Any, int, torch.dtype], int] = lambda spec, page_size, dtype: 0
 
@@ -150,7 +154,7 @@ def _state_allocate(spec, max_requests, _page_size, _dtype, device):
 
 register_cache_kind(KVCacheSpec, CacheKind(
     paged=True, allocate=_kv_allocate, window=lambda spec: spec.window, chunk=lambda spec: spec.chunk,
-    page_bytes=lambda spec, page_size, dtype: spec.kv_heads * (spec.head_dim + (spec.v_dim or spec.head_dim)) * page_size
+    keep_first=lambda spec: spec.keep_first, page_bytes=lambda spec, page_size, dtype: spec.kv_heads * (spec.head_dim + (spec.v_dim or spec.head_dim)) * page_size
     * torch.empty((), dtype=dtype).element_size()))
 register_cache_kind(StateSpec, CacheKind(paged=False, allocate=_state_allocate))
 
@@ -198,6 +202,13 @@ class NormedSum:
     terms: tuple
     coef: float = 1.0
     eps: float = 1e-6
+
+
+@dataclass
+class ScaledSum:
+    """A sublayer's output as sum_i c_i * a_i: `terms` pairs of float [T, hidden] and a number, for a block whose sum
+    kernel forms it on the way into the stream."""
+    terms: tuple
 
 
 @dataclass

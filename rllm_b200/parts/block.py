@@ -4,7 +4,8 @@ order (src/model/registry/llama.rs:163-245): h += mixer(norm(h)); h += ffn(norm(
 the feed-forward, which may be absent. `LoopStep` is a block that only adds a learned vector to
 every row: what a pass of a looped stretch of layers begins with. `PostNormBlock` norms after the sum,
 h = norm(alpha h + sublayer(h)), the sublayers reading the stream itself. `ParallelBlock` has one norm whose
-output both sublayers read: h += mixer(n) + ffn(n), n = norm(h)."""
+output both sublayers read: h += mixer(n) + ffn(n), n = norm(h). `GatedPreNormBlock` is the pre-norm order with a
+gate on each sublayer's way into the stream: h += sigmoid(W_g n + b_g) * sublayer(n), n = norm(h), W_g a square matrix."""
 from __future__ import annotations
 
 from .base import Param, Part, Source, register_part
@@ -189,6 +190,68 @@ class ParallelBlock(Part):
         return ctx.backend.combine(h, m, f)
 
 
+class GatedPreNormBlock(Part):
+    """n = norm1(h); h += sigmoid(W_1 n + b_1) * mixer(n); then the same with norm2, W_2, b_2 and the feed-forward, which
+    may be absent. The gates are as wide as the stream. A sublayer returns its float output (a tensor, or `ScaledSum`
+    for a mixer made of mixers); the gate's sigmoid, the product with the output and the residual sum are one float
+    kernel. `names`: checkpoint sub-prefixes of mixer and feed-forward; `gate_names`: the gates' matrices under the
+    block's prefix (their biases: the same names with `.b`); the norms' weights are tensors named by each norm's
+    `weight_name` under the block's prefix."""
+    graph_safe = True
+
+    def __init__(self, hidden: int, mixer_norm: Part, mixer: Part, ffn_norm: Part | None = None, ffn: Part | None = None,
+                 names=("mix.", "mlp."), gate_names=("rg1", "rg2")):
+        self.hidden, self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = hidden, mixer_norm, mixer, ffn_norm, ffn
+        self.names, self.gate_names = names, gate_names
+        self.w_g1 = self.b_g1 = self.w_g2 = self.b_g2 = None
+
+    def children(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
+
+    def params(self):
+        W = self.hidden
+        g1, g2 = self.gate_names
+        ps = [Param("w_g1", (Source(g1, (W, W)),)), Param("b_g1", (Source(g1 + ".b", (W,)),), role="vector")]
+        if self.ffn is not None:
+            ps += [Param("w_g2", (Source(g2, (W, W)),)), Param("b_g2", (Source(g2 + ".b", (W,)),), role="vector")]
+        return ps
+
+    def set_prefix(self, prefix: str):
+        self.prefix = prefix
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None:
+                norm.prefix = prefix
+        for part, sub in ((self.mixer, self.names[0]), (self.ffn, self.names[1])):
+            if part is None:
+                continue
+            if hasattr(part, "set_prefix"):
+                part.set_prefix(prefix + sub)
+                continue
+            part.prefix = prefix + sub
+            for c in part.children():
+                if not c.prefix:
+                    c.prefix = part.prefix
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def finalize(self, device, dtype):
+        self._b1 = self.b_g1.float().contiguous()
+        self._b2 = None if self.b_g2 is None else self.b_g2.float().contiguous()
+
+    def forward(self, h, ctx, cache):
+        """h: float32 residual stream [T, hidden], updated in place."""
+        be = ctx.backend
+        n = self.mixer_norm.deferred(h, ctx)
+        gate = be.linear_f32(n, self.w_g1, tag="gate")
+        be.gated_add(h, gate, self._b1, self.mixer.forward(n, ctx, cache, None))
+        if self.ffn is not None:
+            n = self.ffn_norm.deferred(h, ctx)
+            gate = be.linear_f32(n, self.w_g2, tag="gate")
+            be.gated_add(h, gate, self._b2, self.ffn.forward(n, ctx, None))
+        return h
+
+
 class LoopStep(Part):
     """h += table[index] on every row. The passes of one loop share the table [times, hidden]: the
     first owns the tensor (`owner` None), the others name the first."""
@@ -218,4 +281,5 @@ register_part("block", "prenorm", PreNormBlock)
 register_part("block", "sandwich", SandwichBlock)
 register_part("block", "postnorm", PostNormBlock)
 register_part("block", "parallel", ParallelBlock)
+register_part("block", "prenorm_gated", GatedPreNormBlock)
 register_part("block", "loop_step", LoopStep)

@@ -1,7 +1,7 @@
 """Dense feed-forwards as parts. `SwiGLU`: down(silu(gate x) * (up x)). Formula:
 src/gpu/cuda/shaders/moe.cu:141-146 and src/model/primitives.rs:557-585 of the reference. Gate and up
 weights are stacked so that one product yields both. `ActFFN`: down(act(up x)) with act = relu(.)^2.
-Both add into the residual stream, or return their float output when `residual` is None (for blocks that
+`ActFFN` also knows act = gelu in its tanh form. Both add into the residual stream, or return their float output when `residual` is None (for blocks that
 norm after the sum)."""
 from __future__ import annotations
 
@@ -33,10 +33,10 @@ class SwiGLU(Part):
 
 
 class ActFFN(Part):
-    """down(act(up x)), no biases; act: "relu2" = max(., 0)^2."""
+    """down(act(up x)), no biases; act: "relu2" = max(., 0)^2, "gelu_tanh" = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))."""
     graph_safe = True
     returns_output = True
-    ACTS = ("relu2",)
+    ACTS = ("relu2", "gelu_tanh")
 
     def __init__(self, hidden: int, intermediate: int, act: str = "relu2", names=("up", "down")):
         if act not in self.ACTS:

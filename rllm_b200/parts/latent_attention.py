@@ -9,7 +9,8 @@ values alike). The up-projections never run over the cache: with
 W_uk is folded into the query before the attention kernel and W_uv applied to its output, both as
 one product per head in one launch. Scores are (plain + rotated part) * `scale`, softmax over the keys
 a `window` allows (None: all earlier ones); each head's output is multiplied by sigmoid of a gate
-projected from h; W_o follows. Scores, softmax, the latent's norm and the rotation are float.
+projected from h (`gate` False: there is none); W_o follows. `rot_dim` 0 with `position` None: no rotated part,
+positions do not enter the scores. Scores, softmax, the latent's norm and the rotation are float.
 """
 from __future__ import annotations
 
@@ -42,18 +43,21 @@ class LatentAttention(Part):
     returns_output = True      # forward(..., residual=None) returns the float output instead of adding it
 
     def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float,
-                 position: Part, window: int | None = None, eps: float = 1e-6):
+                 position: Part | None, window: int | None = None, eps: float = 1e-6, gate: bool = True):
+        if (position is None) != (rot_dim == 0):
+            raise ValueError("a rotated part needs a position part, and only a rotated part does")
         self.hidden, self.heads, self.dim, self.rot_dim, self.vdim = hidden, heads, dim, rot_dim, vdim
         self.kv_rank, self.scale, self.position, self.window, self.eps = kv_rank, float(scale), position, window, float(eps)
+        self.gate = gate
         self.w_in = self.w_latent_norm = self.w_uk = self.w_uv = self.w_o = None
 
     def children(self):
-        return [self.position]
+        return [] if self.position is None else [self.position]
 
     def params(self):
         H, W = self.heads, self.hidden
         return [Param("w_in", (Source("q", (H * (self.dim + self.rot_dim), W)),
-                               Source("dkv", (self.kv_rank + self.rot_dim, W)), Source("g", (H, W)))),
+                               Source("dkv", (self.kv_rank + self.rot_dim, W))) + ((Source("g", (H, W)),) if self.gate else ())),
                 Param("w_latent_norm", (Source("dkv.norm", (self.kv_rank,), init="norm"),), role="vector"),
                 Param("w_uk", (Source("uk", (H * self.dim, self.kv_rank)),)),
                 Param("w_uv", (Source("uv", (H * self.vdim, self.kv_rank)),)),
@@ -76,16 +80,19 @@ class LatentAttention(Part):
         proj = be.linear(x, self.w_in)                                   # [T, q | dkv | gate]
         T = proj.shape[0]
         qfull = torch.empty((T, H, dk), dtype=proj.dtype, device=proj.device)
-        table = self.position.table(ctx)
+        if self.position is None:
+            table, dims = torch.empty((T, 0, 2), dtype=torch.float32, device=proj.device), 0
+        else:
+            table, dims = self.position.table(ctx), self.position.dims
         writes = cache.writes
-        be.latent_prepare(proj, 0, q_cols, H, self.dim, self.rot_dim, self.kv_rank, self.position.dims,
+        be.latent_prepare(proj, 0, q_cols, H, self.dim, self.rot_dim, self.kv_rank, dims,
                           self._norm_f32, self.eps, table, cache.slots if writes else None,
                           cache.tensors["kv"] if writes else None, qfull)
         be.linear_heads(proj, self.dim + self.rot_dim, self._uk_t, qfull.view(T, H * dk), dk)
         o = be.latent_attention(qfull, cache, ctx, self.kv_rank, self.scale, self.window)
         att = torch.empty((T, H * self.vdim), dtype=proj.dtype, device=proj.device)
         be.linear_heads(o.view(T, H * self.kv_rank), self.kv_rank, self._uv, att, self.vdim,
-                        gate=proj[:, q_cols + dk:])
+                        gate=proj[:, q_cols + dk:] if self.gate else None)
         if residual is None:
             return be.linear_f32(att, self.w_o)
         be.linear_residual(att, self.w_o, residual)

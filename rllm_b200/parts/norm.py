@@ -1,5 +1,6 @@
 """RMSNorm as a part. Formula and rounding: src/gpu/cuda/shaders/rms_norm.cu:78-115 of the
-reference (sum of squares and scaling in float, weight used as stored)."""
+reference (sum of squares and scaling in float, weight used as stored). `offset`: the checkpoint stores
+the weight minus this number (weights "around zero": offset 1); the sum is formed once, in float."""
 from __future__ import annotations
 
 from .base import Param, Part, Source, register_part
@@ -8,11 +9,14 @@ from .base import Param, Part, Source, register_part
 class RMSNorm(Part):
     graph_safe = True
 
-    def __init__(self, size: int, eps: float, weight_name: str = "weight"):
-        self.size, self.eps, self.weight_name = size, float(eps), weight_name
-        self.weight = None
+    def __init__(self, size: int, eps: float, weight_name: str = "weight", offset: float = 0.0):
+        self.size, self.eps, self.weight_name, self.offset = size, float(eps), weight_name, float(offset)
+        self.weight = self.stored = None
 
     def params(self):
+        if self.offset:
+            # what the checkpoint holds is bound to `stored`; `weight` is made from it when the weights are bound
+            return [Param("stored", (Source(self.weight_name, (self.size,), init="normal"),), role="vector")]
         return [Param("weight", (Source(self.weight_name, (self.size,), init="norm"),), role="vector")]
 
     def forward(self, h, ctx):
@@ -32,6 +36,8 @@ class RMSNorm(Part):
 
     def finalize(self, device, dtype):
         self._w32 = None            # weights were (re)bound
+        if self.offset:
+            self.weight = (self.stored.float() + self.offset).contiguous()
 
     def forward_f32(self, h, ctx):
         import torch

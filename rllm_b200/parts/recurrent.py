@@ -15,7 +15,12 @@ and silu; q and k become unit vectors per head (q also times dim^-1/2); beta = s
 head and key channel g = exp(-exp(A_log) softplus(W_a2 (W_a1 h) + dt_bias)); per head
     S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q.
 Each head's o is RMS-normed over vdim with one weight shared by the heads, times sigmoid(W_g2 (W_g1 h)), then W_o.
-The widths of the two bottlenecks are sizes of the checkpoint unless given (random-weights mode)."""
+The widths of the two bottlenecks are sizes of the checkpoint unless given (random-weights mode).
+
+`MinGRUMixer` (a gated recurrence whose gates read only the current token; no convolution, the state one number per
+channel). z = sigmoid(W_z h + b_z), u = W_x h + b_x, the candidate c = u + 1/2 where u >= 0 and sigmoid(u) where u < 0;
+    S_t = (1 - z_t) S_(t-1) + z_t c_t,
+and the output is W_o (S_t * silu(W_g h))."""
 from __future__ import annotations
 
 import torch
@@ -137,16 +142,51 @@ class DeltaRuleMixer(Part):
         return None
 
 
+class MinGRUMixer(Part):
+    graph_safe = True
+    returns_output = True
+
+    def __init__(self, hidden: int, width: int, names=("z", "x", "g", "o")):
+        self.hidden, self.width, self.names = hidden, width, names
+        self.w_in = self.b_z = self.b_x = self.w_o = None
+
+    def params(self):
+        W, R = self.hidden, self.width
+        z, x, g, o = self.names
+        return [Param("w_in", (Source(z, (R, W)), Source(x, (R, W)), Source(g, (R, W)))),
+                Param("b_z", (Source(z + ".b", (R,)),), role="vector"),
+                Param("b_x", (Source(x + ".b", (R,)),), role="vector"),
+                Param("w_o", (Source(o, (W, R)),))]
+
+    def cache_spec(self):
+        return StateSpec((("S", (self.width,), torch.float32),))
+
+    def finalize(self, device, dtype):
+        self._bz, self._bx = self.b_z.float().contiguous(), self.b_x.float().contiguous()
+
+    def forward(self, x, ctx, cache, residual=None):
+        be = ctx.backend
+        R = self.width
+        proj = be.linear_f32(x, self.w_in, tag="in")                                # float [T, z | x | g]
+        y = be.mingru_scan(proj, 0, R, 2 * R, R, self._bz, self._bx, ctx, cache.state["S"])
+        if residual is None:
+            return be.linear_f32(y, self.w_o, tag="o")
+        be.linear_residual(y, self.w_o, residual)
+        return None
+
+
 class SideBySideMixer(Part):
     """Two mixers that read the same input; the result is coef * (w_l * l / rms(l) + w_r * r / rms(r)) with plain
     weights `<left name>out` and `<right name>out` of the model's width. Returned as `NormedSum`: the block's sum
-    kernel norms and adds the two. Each member has a cache layer of its own."""
+    kernel norms and adds the two. Each member has a cache layer of its own. `scales` (a_l, a_r): no norms and no
+    weights, the result is a_l * l + a_r * r, returned as `ScaledSum`."""
     graph_safe = True
     returns_output = True
 
     def __init__(self, hidden: int, left: Part, right: Part, coef: float = 0.5, eps: float = 1e-6,
-                 names=("left.", "right.")):
+                 names=("left.", "right."), scales: tuple | None = None):
         self.hidden, self.left, self.right, self.coef, self.eps, self.names = hidden, left, right, float(coef), float(eps), names
+        self.scales = None if scales is None else (float(scales[0]), float(scales[1]))
         self.w_left = self.w_right = None
 
     def children(self):
@@ -158,6 +198,8 @@ class SideBySideMixer(Part):
             part.prefix = prefix + sub
 
     def params(self):
+        if self.scales is not None:
+            return []
         return [Param("w_left", (Source(self.names[0] + "out", (self.hidden,), init="norm"),), role="vector"),
                 Param("w_right", (Source(self.names[1] + "out", (self.hidden,), init="norm"),), role="vector")]
 
@@ -165,17 +207,21 @@ class SideBySideMixer(Part):
         return (self.left.cache_spec(), self.right.cache_spec())
 
     def finalize(self, device, dtype):
-        self._wl, self._wr = self.w_left.float().contiguous(), self.w_right.float().contiguous()
+        if self.scales is None:
+            self._wl, self._wr = self.w_left.float().contiguous(), self.w_right.float().contiguous()
 
     def forward(self, x, ctx, cache, residual=None):
-        from .base import NormedSum
+        from .base import NormedSum, ScaledSum
         if residual is not None:
-            raise NotImplementedError("SideBySideMixer returns its normed summands; the block adds them")
+            raise NotImplementedError("SideBySideMixer returns its summands; the block adds them")
         l = self.left.forward(x, ctx, cache[0], None)
         r = self.right.forward(x, ctx, cache[1], None)
+        if self.scales is not None:
+            return ScaledSum(((l, self.scales[0]), (r, self.scales[1])))
         return NormedSum(((l, self._wl), (r, self._wr)), self.coef, self.eps)
 
 
 register_part("mixer", "state_space", StateSpaceMixer)
 register_part("mixer", "delta_rule", DeltaRuleMixer)
 register_part("mixer", "side_by_side", SideBySideMixer)
+register_part("mixer", "min_gru", MinGRUMixer)
