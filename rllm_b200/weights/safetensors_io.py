@@ -113,7 +113,7 @@ def write_safetensors(path: str, tensors: dict[str, torch.Tensor]) -> None:
         t = t.detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise WeightFileError(f"cannot store dtype {t.dtype}")
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""       # a scalar has a shape of []
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)
