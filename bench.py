@@ -183,11 +183,47 @@ def _bazulorn_sizes():
     return out
 
 
+def _purozen_sizes():
+    """Four layers: sigmoid-weighted attention beside a gated recurrence of the model's width; windowed attention with
+    kept first tokens whose values the fourth layer mixes into its own; attention over latents; windowed attention
+    again. Heads of 128 over four key/value heads, a window of 1,024 with 64 kept tokens (shorter than the prompt,
+    level with the decode context), half of each head rotated, latents of 512 numbers, feed-forwards of four times
+    the width. Beside it four Bazulorn layers of equal width and heads (attention with mixed heads beside a state-space
+    recurrence, two delta-rule layers) with dense gated feed-forwards of the same weights (two thirds the inner size)."""
+    out = {}
+    for name, W, H in (("w2048", 2048, 16), ("w4096", 4096, 32)):
+        ff = {"kind": "dense", "ff": 4 * W}
+        att = {"type": "attention", "mlp": ff, "mixer": {
+            "heads": H, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024, "keep_first": 64},
+            "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0}}, "v_mix": True}}
+        par = {"type": "parallel", "mlp": ff, "mixer": {
+            "left": {"heads": H, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}, "left_scale": 0.5,
+            "right": {"width": W}, "right_scale": 0.5}}
+        lat = {"type": "latent_attention", "mlp": ff,
+               "mixer": {"heads": H, "dim": 128, "vdim": 128, "kv_rank": 512, "scale": 128 ** -0.5}}
+        pz = {"architecture": "Purozen", "vocab": 32000, "width": W, "norm": {"eps": 1e-6}, "layers": [par, att, lat, att]}
+        bff = {"kind": "dense", "ff": 8 * W // 3 // 64 * 64}
+        bpar = {"type": "parallel", "mlp": bff, "mixer": {
+            "left": {"heads": H, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 4096}},
+            "right": {"heads": W // 64, "vdim": 64, "state": 128, "groups": 4, "norm_groups": 4, "conv": 4}}}
+        brec = {"type": "channel_delta", "mlp": bff,
+                "mixer": {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 16, "gate_rank": 64}}
+        bz = {"architecture": "Bazulorn", "vocab": 32000, "width": W, "norm": {"eps": 1e-6}, "layers": [bpar, brec, brec, bpar]}
+        out[name] = (pz, bz)
+    return out
+
+
+BESIDE = {"bazulorn": "zukotar", "purozen": "bazulorn"}       # the design timed beside each one; Llama layers otherwise
+
+
 def design_sizes(design):
     """name -> (the design's configuration, the layers beside it: Llama layers of equal width, depth and active
-    feed-forward weights, or for Bazulorn the Zukotar model of equal width, depth, heads and experts)."""
+    feed-forward weights, for Bazulorn the Zukotar model of equal width, depth, heads and experts, for Purozen
+    Bazulorn layers of equal width, depth and heads)."""
     if design == "livovik":
         return _livovik_sizes()
+    if design == "purozen":
+        return _purozen_sizes()
     if design == "bazulorn":
         zk = design_sizes("zukotar")
         return {name: (cfg, zk[name][0]) for name, cfg in _bazulorn_sizes().items()}
@@ -234,7 +270,7 @@ def compare_designs(design, W, K):
 
     for name, cfgs in design_sizes(design).items():
         res[name] = {}
-        for arch, cfg in zip((design, "zukotar" if design == "bazulorn" else "llama"), cfgs):
+        for arch, cfg in zip((design, BESIDE.get(design, "llama")), cfgs):
             vocab = cfg.get("vocab", cfg.get("vocab_size"))
             prompt = [(7 * i + 3) % vocab for i in range(T)]
             r = {}
@@ -289,9 +325,10 @@ def main():
     ap.add_argument("--workloads", default="", help="comma-separated: mixed_3b, continuous_8b, or all")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (for profiling; the JSON line then lacks the other parts)")
-    ap.add_argument("--designs", default="", choices=["", "zukotar", "livovik", "bazulorn"],
+    ap.add_argument("--designs", default="", choices=["", "zukotar", "livovik", "bazulorn", "purozen"],
                     help="instead of the default workload: prefill and decode of this design beside Llama layers of "
-                         "equal size (bazulorn: beside Zukotar layers), random weights, with the time per operation; "
+                         "equal size (bazulorn: beside Zukotar layers; purozen: beside Bazulorn layers), random weights, "
+                         "with the time per operation; "
                          "prints its own JSON line")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket one timed step with cudaProfilerStart/Stop (ncu --profile-from-start off)")

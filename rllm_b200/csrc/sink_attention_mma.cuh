@@ -50,6 +50,11 @@ __device__ __forceinline__ float fast_exp2(float x) {          // exp2(-inf) = 0
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float fast_rcp(float x) {           // 1 / inf = 0; relative error about 2^-23
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -264,8 +269,8 @@ __global__ void __launch_bounds__(THREADS) sink_attention_mma_kernel(const Args 
       // sigmoid(x) = 1 / (1 + 2^(-x log2 e)); a masked key's -inf gives 1 / (1 + inf) = 0
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        sc[nt][0] = __frcp_rn(1.f + fast_exp2(-(sc[nt][0] + sb0))); sc[nt][1] = __frcp_rn(1.f + fast_exp2(-(sc[nt][1] + sb0)));
-        sc[nt][2] = __frcp_rn(1.f + fast_exp2(-(sc[nt][2] + sb1))); sc[nt][3] = __frcp_rn(1.f + fast_exp2(-(sc[nt][3] + sb1)));
+        sc[nt][0] = fast_rcp(1.f + fast_exp2(-(sc[nt][0] + sb0))); sc[nt][1] = fast_rcp(1.f + fast_exp2(-(sc[nt][1] + sb0)));
+        sc[nt][2] = fast_rcp(1.f + fast_exp2(-(sc[nt][2] + sb1))); sc[nt][3] = fast_rcp(1.f + fast_exp2(-(sc[nt][3] + sb1)));
       }
     } else {
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));

@@ -79,7 +79,7 @@ struct Params {
   void* C;                  // output [T][N] (type by epilogue), row stride ldc
   long long ldc;
   int T;
-  int act;                  // store epilogue only: 1 stores max(value, 0)^2
+  int act;                  // store epilogue only: 1 stores max(value, 0)^2, 2 gelu(value) in its tanh form
   int njobs;
   int nchw;                 // chunks per warp and tile
   RopeArgs rope;
@@ -313,7 +313,12 @@ stream_gemm_kernel(const Params p) {
         }
       } else {
         const size_t o = (size_t)tok * p.ldc + job * 16 + r;
-        if (EPI == EPI_STORE) ((bf16*)p.C)[o] = __float2bfloat16_rn(p.act ? fmaxf(s0, 0.f) * fmaxf(s0, 0.f) : s0);
+        if (EPI == EPI_STORE) {
+          float v = s0;
+          if (p.act == 1) v = fmaxf(s0, 0.f) * fmaxf(s0, 0.f);
+          else if (p.act == 2) v = s0 / (1.f + expf(-1.5957691216057308f * (s0 + 0.044715f * s0 * s0 * s0)));   // = 0.5 s (1 + tanh(.))
+          ((bf16*)p.C)[o] = __float2bfloat16_rn(v);
+        }
         else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = s0;
         else if (EPI == EPI_ACCUM_F32) ((float*)p.C)[o] += s0;
         else if (EPI == EPI_SWIGLU) ((bf16*)p.C)[o] = __float2bfloat16_rn(s0 / (1.f + expf(-s0)) * s1);
@@ -402,9 +407,9 @@ RLLM_API int rllm_stream_gemm_supported(int epi, int norm, int T, int N, int K, 
 RLLM_API int rllm_stream_gemm(int epi, const void* X, long long ldx, const float* h, long long ldh, const int* rows,
                               const void* g, int g_dt, float eps, const void* W, void* Cout, long long ldc,
                               int T, int N, int K, int sm_count, void* stream) {
-  const int act = epi >> 8;                       // as in rllm_tc_gemm: 0 | 1 << 8 stores max(value, 0)^2
+  const int act = epi >> 8;                       // as in rllm_tc_gemm: 0 | 1 << 8 stores max(value, 0)^2, 0 | 2 << 8 gelu(value)
   epi &= 0xff;
-  if (epi < 0 || epi > EPI_SWIGLU || act > 1 || (act && epi != EPI_STORE)) return ERR_BAD_SIZE;
+  if (epi < 0 || epi > EPI_SWIGLU || act > 2 || (act && epi != EPI_STORE)) return ERR_BAD_SIZE;
   const bool norm = X == nullptr;
   if (norm && (!h || !g || (g_dt != DT_F32 && g_dt != DT_BF16))) return ERR_BAD_SIZE;
   Params p = {};

@@ -154,7 +154,7 @@ struct Params {
   int splits;         // CTAs per cluster = ranges of K
   int bn;             // persistent kernel: tokens per tile (a multiple of 16, at most the template's BN)
   int* err;           // device error word (0 = fine)
-  int act;            // store epilogue only: 0 the value as it is, 1 max(value, 0)^2
+  int act;            // store epilogue only: 0 the value as it is, 1 max(value, 0)^2, 2 gelu in its tanh form
   RopeArgs rope;
   NormArgs norm;      // NORM variants only
 };
@@ -162,7 +162,9 @@ struct Params {
 static thread_local int t_store_act = 0;     // host side: the activation of the call being launched (see StoreAct)
 
 __device__ __forceinline__ float store_act(const Params& p, float v) {
-  if (p.act) { v = fmaxf(v, 0.f); v *= v; }
+  if (p.act == 1) { v = fmaxf(v, 0.f); v *= v; }
+  // 0.5 v (1 + tanh(u)) = v / (1 + exp(-2u)), u = sqrt(2/pi) (v + 0.044715 v^3)
+  else if (p.act == 2) v = __fdividef(v, 1.f + __expf(-1.5957691216057308f * (v + 0.044715f * v * v * v)));
   return v;
 }
 
@@ -1537,9 +1539,12 @@ RLLM_API int rllm_tc_gemm_set_pairs(int on) { g_pairs = on != 0; return 0; }
 RLLM_API int rllm_tc_gemm_set_token_rows(int on) { g_token_rows = on != 0; return 0; }
 
 // The store epilogue (0) may carry an activation in the bits above the epilogue's number: epi = 0 | 1 << 8 stores
-// max(value, 0)^2. The launcher's own state for one call:
+// max(value, 0)^2, 0 | 2 << 8 gelu(value) in its tanh form. The launcher's own state for one call:
 struct StoreAct {
-  explicit StoreAct(int& epi) { t_store_act = (epi >> 8) == 1 && (epi & 0xff) == EPI_STORE; epi = (epi >> 8) > 1 ? -1 : (epi & 0xff); }
+  explicit StoreAct(int& epi) {
+    t_store_act = (epi & 0xff) == EPI_STORE ? (epi >> 8) : 0;
+    epi = ((epi >> 8) > 2 || ((epi >> 8) && (epi & 0xff) != EPI_STORE)) ? -1 : (epi & 0xff);
+  }
   ~StoreAct() { t_store_act = 0; }
 };
 

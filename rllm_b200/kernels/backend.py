@@ -279,13 +279,16 @@ class Backend:
     def linear_act(self, x, w, act):
         """act(x W^T) in the run dtype; act "relu2" = max(., 0)^2, "gelu_tanh" = gelu in its tanh form (on the float
         product, rounded once)."""
+        if act not in ("relu2", "gelu_tanh"):
+            raise ops.KernelError(f"activation {act!r} has no kernel")
+        fuse = os.environ.get("RLLM_B200_NO_ACT_FUSION") != "1"
+        if fuse and self._fused_norm(x, w):                                  # the norm in front, the activation behind
+            return self._sm100.gemm_norm(x.h, x.weight, x.eps, w, ops.EPI_STORE, rows=x.rows, act=act)
+        x = x.tensor() if isinstance(x, Normed) else x
+        if self._tc(x, w) and fuse:
+            return self._sm100.gemm(x, w, ops.EPI_STORE, act=act)            # in the product's store epilogue
         if act == "gelu_tanh":
             return self._hy.act_rows(self.linear_f32(x, w, tag="up"), self.dtype, act)
-        if act != "relu2":
-            raise ops.KernelError(f"activation {act!r} has no kernel")
-        x = x.tensor() if isinstance(x, Normed) else x
-        if self._tc(x, w) and os.environ.get("RLLM_B200_NO_ACT_FUSION") != "1":
-            return self._sm100.gemm(x, w, ops.EPI_STORE, relu2=True)        # in the product's store epilogue
         if self._tc(x, w):
             return self._sink.relu2_(self._sm100.gemm(x, w, ops.EPI_STORE))
         return ops.gemm_simt(x, w, ops.EPI_RELU2)

@@ -399,6 +399,83 @@ def cmd_scan(a) -> None:
             return
 
 
+def cmd_gated(a) -> None:
+    """The kernels of layers whose sublayers are gated into the stream, each beside its like kernel at the same sizes:
+    attention with sigmoid weights and with kept first keys beside the softmax and the window alone (one kernel, other
+    branches), the gated recurrence beside the state scan, the gated sum beside the sum of a layer's terms, the gelu in
+    a product's epilogue beside relu squared there."""
+    from . import hybrid, sink
+    nh, nkv, kd, vd, page, W = a.heads, a.kv_heads, a.dim, a.vdim, a.page, a.width
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    bf = lambda *shape: torch.randn(*shape, device=DEV, dtype=torch.bfloat16)
+    bias, scale = torch.randn(nh, device=DEV) - 2, kd ** -0.5
+    for T in a.tokens:                                   # one prompt of T tokens
+        pages = (T + page - 1) // page
+        kc, vc = bf(pages, nkv, page, kd), bf(pages, nkv, page, vd)
+        bt, cu = torch.arange(pages, device=DEV, dtype=torch.int32).view(1, pages), i32([0, T])
+        q = bf(T, nh * kd)
+        pos, seq = torch.arange(T, device=DEV, dtype=torch.int32), torch.zeros(T, device=DEV, dtype=torch.int32)
+        pairs = T * (T + 1) / 2
+        run([lambda: sink.sink_attention_mma(q, kc, vc, seq, pos, bt, cu, 1, T, nh, scale, None, None, bias, None, 1, T, 0, True)] * 4,
+            a.plain, f"sigmoid attention (mma.sync) T={T} heads={nh}/{nkv} of {kd}/{vd}", flops=2.0 * nh * (kd + vd) * pairs)
+        if a.plain:
+            return
+        run([lambda: sink.sink_attention_mma(q, kc, vc, seq, pos, bt, cu, 1, T, nh, scale, None, None, None, None, 1, T)] * 4, 0,
+            f"  like: softmax attention, the same kernel T={T}", flops=2.0 * nh * (kd + vd) * pairs)
+        win, kept = a.window, a.keep_first
+        wpairs = sum(min(i + 1, win) + min(kept, max(0, i + 1 - win)) for i in range(T))
+        run([lambda: sink.sink_attention_mma(q, kc, vc, seq, pos, bt, cu, 1, T, nh, scale, win, None, None, None, 1, T, kept)] * 4, 0,
+            f"windowed attention with kept first keys T={T} window={win} kept={kept}", flops=2.0 * nh * (kd + vd) * wpairs)
+        run([lambda: sink.sink_attention_mma(q, kc, vc, seq, pos, bt, cu, 1, T, nh, scale, win, None, None, None, 1, T)] * 4, 0,
+            f"  like: the window alone T={T}", flops=2.0 * nh * (kd + vd) * sum(min(i + 1, win) for i in range(T)))
+        # the gated recurrence beside the state scan over as many channels (heads of 128 x 64 hold 64 times the state)
+        R = a.channels or W
+        proj, bz, bx = torch.randn(T, 3 * R, device=DEV), torch.randn(R, device=DEV), torch.randn(R, device=DEV)
+        st, slots = torch.zeros(1, R, device=DEV), i32([0])
+        run([lambda: hybrid.mingru_scan(proj, 0, R, 2 * R, R, bz, bx, cu, 1, slots, st, torch.bfloat16, T)] * 4, 0,
+            f"gated recurrence T={T} channels={R}", nbytes=T * R * (5 * 4 + 2))
+        H, d, v = max(1, R // 64), 128, 64
+        sq, sk = torch.randn(T, H * d, device=DEV) * d ** -0.5, torch.randn(T, H * d, device=DEV) * d ** -0.5
+        sx, decay, S = torch.randn(T, H * v, device=DEV), torch.rand(T, H, device=DEV) * 0.1 + 0.9, torch.zeros(1, H, d, v, device=DEV)
+        run([lambda: hybrid.state_scan(sq, H, sk, H, sx, decay, H, d, v, cu, 1, slots, S)] * 4, 0,
+            f"  like: state scan T={T}, {H} heads of {d} x {v}", nbytes=T * H * (2 * d + 2 * v) * 4 + decay.numel() * 4)
+        # the gated sum beside the sum of a layer's terms
+        h, g, b, y0, y1 = (torch.randn(T, W, device=DEV) for _ in range(5))
+        run([lambda: hybrid.gated_add(h, g, b[0].contiguous(), [(y0, 0.5), (y1, 0.5)])] * 4, 0,
+            f"gated sum into the stream, two summands T={T} width={W}", nbytes=T * W * 4 * 5)
+        wl = torch.ones(W, device=DEV)
+        run([lambda: hybrid.combine(h, [(y0, wl), (y1, wl)], 0.5, 1e-6, [g])] * 4, 0, f"  like: sum of a layer's terms T={T}",
+            nbytes=T * W * 4 * 5)
+        # gelu in the epilogue of the up product beside relu squared there, and beside the float product with a pass after it
+        x, wu = bf(T, W), bf(4 * W, W)
+        for act in ("gelu_tanh", "relu2"):
+            run([lambda act=act: sm100.gemm(x, wu, ops.EPI_STORE, act=act)] * 4, 0,
+                f"{'  like: ' if act == 'relu2' else ''}up product with {act} in its epilogue T={T} {W} -> {4 * W}", flops=2.0 * T * W * 4 * W)
+        run([lambda: hybrid.act_rows(sm100.gemm(x, wu, ops.EPI_STORE_F32), torch.bfloat16, "gelu_tanh")] * 4, 0,
+            f"  the float product and a pass for the gelu T={T}", flops=2.0 * T * W * 4 * W)
+    for B in a.batch:                                    # B single tokens at context C
+        C = a.context
+        pages = (C + page - 1) // page
+        copies = max(1, min(8, int(2e9 // (B * pages * nkv * page * (kd + vd) * 2))))
+        caches = [(bf(B * pages, nkv, page, kd), bf(B * pages, nkv, page, vd)) for _ in range(copies)]
+        bt = torch.randperm(B * pages, device=DEV).to(torch.int32).view(B, pages).contiguous()
+        pos, seq, cu = i32([C - 1] * B), torch.arange(B, device=DEV, dtype=torch.int32), torch.arange(B + 1, device=DEV, dtype=torch.int32)
+        q = bf(B, nh * kd)
+        tiles = B * nkv * ((nh // nkv + 63) // 64)
+        sp = max(1, min(16, 4 * sm100.init(DEV).sm_count // tiles, C // 128))
+        for sig in (True, False):
+            run([(lambda c=c: sink.sink_attention_mma(q, c[0], c[1], seq, pos, bt, cu, B, 1, nh, scale, None, None, bias if sig else None,
+                                                      None, sp, C, 0, sig)) for c in caches], 0,
+                f"{'sigmoid attention' if sig else '  like: softmax attention'} {B} x 1 token, {C} keys, heads of {kd}/{vd}, ranges={sp}",
+                nbytes=B * C * nkv * (kd + vd) * 2)
+        R = a.channels or W
+        proj, bz, bx = torch.randn(B, 3 * R, device=DEV), torch.randn(R, device=DEV), torch.randn(R, device=DEV)
+        states = [torch.zeros(B, R, device=DEV) for _ in range(8)]
+        run([lambda s=s: hybrid.mingru_scan(proj, 0, R, 2 * R, R, bz, bx, cu, B, seq, s, torch.bfloat16, 1) for s in states], 0,
+            f"gated recurrence {B} x 1 token, channels={R}", nbytes=B * R * (3 * 4 + 2 + 8))
+    sm100.check_error(DEV)
+
+
 def main(argv=None) -> int:
     ints = lambda s: [int(x) for x in s.split(",")]
     ap = argparse.ArgumentParser(prog="python -m rllm_b200.kernels.microbench", description=__doc__.split("\n\n")[0])
@@ -439,6 +516,13 @@ def main(argv=None) -> int:
     p.add_argument("--batch", type=ints, default=[8, 64])
     for k, v in (("heads", 32), ("kv-heads", 8), ("dim", 64), ("vdim", 32), ("page", 16), ("context", 1024), ("chunk", 0),
                  ("width", 2048)):
+        p.add_argument("--" + k, type=int, default=v)
+    p = sub.add_parser("gated")
+    p.add_argument("--plain", type=int, default=0, help="N plain launches of the sigmoid attention kernel instead of timing")
+    p.add_argument("--tokens", type=ints, default=[2048])
+    p.add_argument("--batch", type=ints, default=[8, 64])
+    for k, v in (("heads", 16), ("kv-heads", 4), ("dim", 128), ("vdim", 128), ("page", 16), ("context", 1024), ("window", 1024),
+                 ("keep-first", 64), ("width", 2048), ("channels", 0)):
         p.add_argument("--" + k, type=int, default=v)
     p = sub.add_parser("talk")
     p.add_argument("--plain", type=int, default=0, help="N plain launches of the prompt kernel instead of timing")
@@ -492,7 +576,7 @@ def main(argv=None) -> int:
         return 1
     {"gemm": cmd_gemm, "attn-decode": cmd_attn_decode, "attn-prefill": cmd_attn_prefill, "sample": cmd_sample,
      "experts": cmd_experts, "latent-attn": cmd_latent_attn, "gla": cmd_gla, "sink": cmd_sink, "talk": cmd_talk,
-     "scan": cmd_scan}[a.cmd](a)
+     "scan": cmd_scan, "gated": cmd_gated}[a.cmd](a)
     return 0
 
 

@@ -187,7 +187,7 @@ class OpProfile:
     def qk_norm_rope_store(self, proj, *a, **k):
         return self._timed("qk_norm+rope", 2 * _nbytes(proj), 0, self._be.qk_norm_rope_store, proj, *a, **k)
 
-    def sink_attention(self, q, cache, ctx, nh, scale, window, chunk, sinks, gate):
+    def sink_attention(self, q, cache, ctx, nh, scale, window, chunk, sinks, gate, keep_first=0, sigmoid=False):
         kd, vd, nkv = cache.k.shape[3], cache.v.shape[3], cache.k.shape[1]
         lens, qs = ctx.kv_lens_host, ctx.q_lens_host
         if lens is None:
@@ -199,12 +199,12 @@ class OpProfile:
                 lo = max(0, pos - window + 1) if window else 0
                 if chunk:
                     lo = max(lo, pos // chunk * chunk)
-                pairs += pos - lo + 1
+                pairs += pos - lo + 1 + min(keep_first, lo)
                 first = min(first, lo)
-            seen_keys += n - first
+            seen_keys += n - first + min(keep_first, first)
         nbytes = seen_keys * nkv * (kd + vd) * cache.k.element_size() + _nbytes(q) + q.shape[0] * nh * vd * q.element_size()
-        return self._timed("attention", nbytes, 2 * nh * (kd + vd) * pairs, self._be.sink_attention, q, cache, ctx, nh, scale,
-                           window, chunk, sinks, gate)
+        return self._timed("sigmoid_attention" if sigmoid else "attention", nbytes, 2 * nh * (kd + vd) * pairs,
+                           self._be.sink_attention, q, cache, ctx, nh, scale, window, chunk, sinks, gate, keep_first, sigmoid)
 
     def latent_prepare(self, proj, *a, **k):
         return self._timed("latent_prepare", 2 * _nbytes(proj), 0, self._be.latent_prepare, proj, *a, **k)
@@ -286,6 +286,21 @@ class OpProfile:
         nbytes = sum(seen) * nkv * (kd + vd) * cache.k.element_size() + _nbytes(q) + q.shape[0] * nh * vd * q.element_size()
         return self._timed("talk_attention", nbytes, 2 * nh * (kd + vd) * pairs, self._be.talk_attention, q, cache, ctx, nh,
                            scale, mix, window, chunk, sinks)
+
+    def gated_add(self, h, gate, bias, y):
+        n = 3 + (len(y.terms) if hasattr(y, "terms") else 1)       # the stream read and written, the gate, the summands
+        return self._timed("gate+add", n * _nbytes(h), 0, self._be.gated_add, h, gate, bias, y)
+
+    def mix_values(self, proj, v_off, n_cols, first, lam):
+        return self._timed("value_mix", 3 * proj.shape[0] * n_cols * proj.element_size(), 0, self._be.mix_values, proj, v_off,
+                           n_cols, first, lam)
+
+    def mingru_scan(self, proj, z_off, x_off, g_off, width, bias_z, bias_x, ctx, state):
+        T = proj.shape[0]
+        pieces = 2 if ctx.max_q_len > 64 else 1                    # long portions read the gates' logits twice
+        nbytes = T * width * (4 * (1 + 2 * pieces) + self._be.dtype.itemsize) + 8 * ctx.num_seqs * width
+        return self._timed("gru_scan", nbytes, 0, self._be.mingru_scan, proj, z_off, x_off, g_off, width, bias_z, bias_x, ctx,
+                           state)
 
     def argmax(self, logits):
         return self._timed("sample", _nbytes(logits), 0, self._be.argmax, logits)

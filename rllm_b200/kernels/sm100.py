@@ -125,16 +125,20 @@ def plan(epilogue: int, T: int, N: int, K: int, device="cuda:0", split: bool | i
 
 
 ACT_RELU2 = 1 << 8          # added to the store epilogue's number: max(value, 0)^2 is stored
+ACT_GELU_TANH = 2 << 8      # likewise: gelu(value) in its tanh form
+STORE_ACTS = {None: 0, "relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH}
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, epilogue: int, out: torch.Tensor | None = None,
-         split: bool = True, relu2: bool = False) -> torch.Tensor:
+         split: bool = True, relu2: bool = False, act: str | None = None) -> torch.Tensor:
     """C = X W^T on the tensor cores. x [T, K] bf16 (unit inner stride); w [N, K] bf16 ([2N, K] with
-    the SwiGLU epilogue). `out` is required for the accumulate epilogue (the float residual). `relu2`
-    (store epilogue only): max(., 0)^2 of the float result is what is rounded and stored."""
-    if relu2 and epilogue != ops.EPI_STORE:
-        raise ops.KernelError("tc gemm: relu^2 goes with the store epilogue only")
-    code = epilogue | (ACT_RELU2 if relu2 else 0)
+    the SwiGLU epilogue). `out` is required for the accumulate epilogue (the float residual). `act`
+    (store epilogue only; `relu2` True is act "relu2"): the activation of the float result is what is rounded and
+    stored: "relu2" max(., 0)^2, "gelu_tanh" gelu in its tanh form."""
+    act = "relu2" if relu2 else act
+    if act is not None and (epilogue != ops.EPI_STORE or act not in STORE_ACTS):
+        raise ops.KernelError("tc gemm: an activation (relu2, gelu_tanh) goes with the store epilogue only")
+    code = epilogue | STORE_ACTS[act]
     if not gemm_supported(x, w):
         raise ops.KernelError("tc gemm: operands must be bfloat16, K a multiple of 8, 16-byte aligned")
     st = init(x.device)
@@ -183,8 +187,10 @@ def norm_supported(h: torch.Tensor, g: torch.Tensor, w: torch.Tensor, rows: torc
 
 
 def gemm_norm(h: torch.Tensor, g: torch.Tensor, eps: float, w: torch.Tensor, epilogue: int,
-              rows: torch.Tensor | None = None, split: bool = True) -> torch.Tensor:
-    """C = rmsnorm(h[rows]; g, eps) W^T in one kernel (store, store-float or SwiGLU epilogue)."""
+              rows: torch.Tensor | None = None, split: bool = True, act: str | None = None) -> torch.Tensor:
+    """C = rmsnorm(h[rows]; g, eps) W^T in one kernel (store, store-float or SwiGLU epilogue; `act` as in `gemm`)."""
+    if act is not None and (epilogue != ops.EPI_STORE or act not in STORE_ACTS):
+        raise ops.KernelError("tc gemm with norm: an activation (relu2, gelu_tanh) goes with the store epilogue only")
     if not norm_supported(h, g, w, rows):
         raise ops.KernelError("tc gemm with norm: float32 rows of K % 8 == 0 values, at most "
                               f"{norm_max_tokens()} tokens, bfloat16 weights, 16-byte aligned")
@@ -198,12 +204,12 @@ def gemm_norm(h: torch.Tensor, g: torch.Tensor, eps: float, w: torch.Tensor, epi
                       device=h.device)
     if split and stream_supported(epilogue, True, T, N, K):
         rc = ops._fn("sm100", "rllm_stream_gemm")(
-            epilogue, None, 0, h.data_ptr(), h.stride(0), ops._ptr(rows), g.data_ptr(), ops._dt(g, "norm weight"),
+            epilogue | STORE_ACTS[act], None, 0, h.data_ptr(), h.stride(0), ops._ptr(rows), g.data_ptr(), ops._dt(g, "norm weight"),
             float(eps), w.data_ptr(), out.data_ptr(), out.stride(0), T, N, K, st.sm_count, ops._stream())
         ops._check(rc, "stream_gemm_norm")
         return out
     rc = ops._fn("sm100", "rllm_tc_gemm_norm")(
-        epilogue, h.data_ptr(), h.stride(0), ops._ptr(rows), g.data_ptr(), ops._dt(g, "norm weight"), float(eps),
+        epilogue | STORE_ACTS[act], h.data_ptr(), h.stride(0), ops._ptr(rows), g.data_ptr(), ops._dt(g, "norm weight"), float(eps),
         w.data_ptr(), out.data_ptr(), out.stride(0), T, N, K, int(split), st.err.data_ptr(), st.sm_count,
         ops._stream())
     ops._check(rc, "tc_gemm_norm")

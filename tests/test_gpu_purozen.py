@@ -121,6 +121,24 @@ def test_gelu_rows_and_values_mixed_in_place(dtype):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("T,K,N", [(3, 64, 96), (40, 128, 320), (300, 256, 512), (5, 72, 100)])
+def test_gelu_behind_a_product_with_and_without_the_norm_in_front(dtype, T, K, N):
+    """act(x W^T) as the feed-forward asks for it: in bfloat16 the activation runs on the float accumulator in the
+    product's epilogue (few tokens: the norm in front of the same kernel), rounded once."""
+    from rllm_b200.kernels.backend import Backend
+    be = Backend(DT[dtype], DEV)
+    h, g, w = rnd(T, K, seed=1, scale=2.0), rnd(K, seed=2, scale=0.2) + 1, rnd(N, K, seed=3, scale=0.2)
+    ws = w.to(DT[dtype])
+    n = P.unit_rms(h.double(), 1e-5) * g.double()
+    tol = 2e-5 if dtype == "float32" else 1.5e-2
+    got = be.linear_act(be.normed(h.to(DEV), g.to(DEV), 1e-5), ws.to(DEV), "gelu_tanh")
+    assert got.dtype == DT[dtype] and rel(got, P.gelu_tanh(stored_as(dtype)(n) @ ws.double().T)) < tol
+    x = n.to(DT[dtype])
+    got = be.linear_act(x.to(DEV), ws.to(DEV), "gelu_tanh")
+    assert rel(got, P.gelu_tanh(x.double() @ ws.double().T)) < tol
+
+
+@pytest.mark.parametrize("dtype", list(DT))
 def test_norm_weight_stored_around_zero_is_added_in_float(dtype):
     """Stored weights of a few thousandths: 1 + w formed in 16 bits would lose them."""
     from rllm_b200.parts import RMSNorm
