@@ -4,8 +4,6 @@
 // gated_add: h[t, c] += sigmoid(g[t, c] + b[c]) * (c0 * y0[t, c] + c1 * y1[t, c])   (y1 may be absent)
 //   the sublayer's output, the gate on it and the residual sum in one pass over the row.
 // act_rows: out[r, f] = act(in[r, f]); 0: gelu in its tanh form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
-// lerp_cols: dst[t, c] = (1 - lam) dst[t, c] + lam src[t, c] for the first n columns of rows with strides of their
-//   own; lam is read from the device.
 // mingru_scan: per channel c of a sequence, with z = sigmoid(pz + bz), u = px + bx,
 //   cand = u + 1/2 where u >= 0 and sigmoid(u) where u < 0:
 //       S_t = (1 - z_t) S_(t-1) + z_t cand_t,     out_t = S_t * silu(pg_t).
@@ -72,20 +70,6 @@ __global__ void act_rows_kernel(const TI* __restrict__ in, long long ld, TO* __r
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const float z = to_f32(in[i / F * ld + i % F]);
     out[i] = from_f32<TO>(gelu_tanh_(z));
-  }
-}
-
-template <typename T>
-__global__ void lerp_cols_kernel(T* __restrict__ dst, long long ldd, const T* __restrict__ src, long long lds, int n_cols,
-                                 long long n, const float* __restrict__ lam) {
-  pdl_launch();
-  pdl_wait();
-  const float l = lam[0];
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / n_cols;
-    const int c = (int)(i % n_cols);
-    const float a = to_f32(dst[t * ldd + c]), b = to_f32(src[t * lds + c]);
-    dst[t * ldd + c] = from_f32<T>(fmaf(l, b, (1.f - l) * a));
   }
 }
 
@@ -207,20 +191,6 @@ RLLM_API int rllm_act_rows(const void* in, int in_dt, long long ld, void* out, i
     return launch_ex(act_rows_kernel<float, bf16>, g, b, 0, s, 1, (const float*)in, ld, (bf16*)out, F, n, kind);
   if (in_dt == DT_BF16 && out_dt == DT_BF16)
     return launch_ex(act_rows_kernel<bf16, bf16>, g, b, 0, s, 1, (const bf16*)in, ld, (bf16*)out, F, n, kind);
-  return ERR_BAD_DTYPE;
-}
-
-RLLM_API int rllm_lerp_cols(int dt, void* dst, long long ldd, const void* src, long long lds, int T, int n_cols,
-                            const float* lam, void* stream) {
-  if (T <= 0 || n_cols <= 0) return 0;
-  if (!lam) return ERR_BAD_SIZE;
-  const long long n = (long long)T * n_cols;
-  cudaStream_t s = (cudaStream_t)stream;
-  const dim3 g(blocks_for(n)), b(256);
-  if (dt == DT_F32)
-    return launch_ex(lerp_cols_kernel<float>, g, b, 0, s, 1, (float*)dst, ldd, (const float*)src, lds, n_cols, n, lam);
-  if (dt == DT_BF16)
-    return launch_ex(lerp_cols_kernel<bf16>, g, b, 0, s, 1, (bf16*)dst, ldd, (const bf16*)src, lds, n_cols, n, lam);
   return ERR_BAD_DTYPE;
 }
 

@@ -11,7 +11,8 @@
 //     sigmoid(score + bias[head]), not normalised over the keys (`sinks` then holds the biases);
 //   * an output gate: head h's output times sigmoid(gate[t, h]).
 //
-// qk_norm_rope_store prepares a step's queries (in place) and writes its keys and values into their pages;
+// qk_norm_rope_store prepares a step's queries (in place) and writes its keys and values into their pages, the values
+// optionally mixed with another layer's of the same tokens on the way: v <- (1 - lam) v + lam v_first (float, one rounding);
 // sink_attention_simt is the attention itself on the CUDA cores, in float whatever the storage type (the
 // 32-bit path, and sizes the tensor-core kernel refuses); sink_attention_mma (sink_attention_mma.cuh) is the
 // bfloat16 kernel on the tensor cores. A query's result depends on its position and the cache's contents
@@ -29,7 +30,8 @@ __global__ void __launch_bounds__(128)
 qk_norm_rope_store_kernel(T* __restrict__ proj, long long ld, int q_off, int k_off, int v_off, int n_tokens, int nh,
                           int nkv, int kd, int vd, int rot, const float* __restrict__ wq, const float* __restrict__ wk,
                           float eps, const float* __restrict__ table, const int* __restrict__ slots,
-                          T* __restrict__ kcache, T* __restrict__ vcache, int page_size) {
+                          T* __restrict__ kcache, T* __restrict__ vcache, int page_size, const T* __restrict__ vfirst,
+                          long long ldf, const float* __restrict__ lam) {
   pdl_launch();
   pdl_wait();
   __shared__ float xs[4][MAX_D];
@@ -45,7 +47,13 @@ qk_norm_rope_store_kernel(T* __restrict__ proj, long long ld, int q_off, int k_o
     const int g = u - nh - nkv;
     const T* src = row + v_off + g * vd;
     T* dst = vcache + (((long long)(slot / page_size) * nkv + g) * page_size + slot % page_size) * vd;
-    for (int d = lane; d < vd; d += 32) dst[d] = src[d];
+    if (vfirst) {
+      const float l = lam[0];
+      const T* first = vfirst + (long long)t * ldf + g * vd;
+      for (int d = lane; d < vd; d += 32) dst[d] = from_f32<T>(fmaf(l, to_f32(first[d]), (1.f - l) * to_f32(src[d])));
+    } else {
+      for (int d = lane; d < vd; d += 32) dst[d] = src[d];
+    }
     return;
   }
   const bool is_q = u < nh;
@@ -81,7 +89,8 @@ __global__ void __launch_bounds__(128)
 qk_norm_rope_store_vec_kernel(bf16* __restrict__ proj, long long ld, int q_off, int k_off, int v_off, int n_tokens, int nh,
                               int nkv, int kd, int vd, int rot, const float* __restrict__ wq, const float* __restrict__ wk,
                               float eps, const float* __restrict__ table, const int* __restrict__ slots,
-                              bf16* __restrict__ kcache, bf16* __restrict__ vcache, int page_size) {
+                              bf16* __restrict__ kcache, bf16* __restrict__ vcache, int page_size,
+                              const bf16* __restrict__ vfirst, long long ldf, const float* __restrict__ lam) {
   pdl_launch();
   pdl_wait();
   constexpr int HPW = 32 / LPH;                      // heads a warp
@@ -103,6 +112,8 @@ qk_norm_rope_store_vec_kernel(bf16* __restrict__ proj, long long ld, int q_off, 
   uint4 own = make_uint4(0, 0, 0, 0), other = make_uint4(0, 0, 0, 0);
   if (mine) own = *reinterpret_cast<const uint4*>(src + c * 8);
   if (turns) other = *reinterpret_cast<const uint4*>(src + cp * 8);
+  const bool mixes = mine && is_v && vfirst;          // a value piece: the other layer's piece of the same token and head
+  if (mixes) other = *reinterpret_cast<const uint4*>(vfirst + (long long)t * ldf + (u - nh - nkv) * vd + c * 8);
   float x[8], y[8];
   {
     const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&own);
@@ -129,6 +140,11 @@ qk_norm_rope_store_vec_kernel(bf16* __restrict__ proj, long long ld, int q_off, 
       y[0] *= r * p0.x; y[1] *= r * p0.y; y[2] *= r * p0.z; y[3] *= r * p0.w;
       y[4] *= r * p1.x; y[5] *= r * p1.y; y[6] *= r * p1.z; y[7] *= r * p1.w;
     }
+  }
+  if (mixes) {
+    const float l = lam[0];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = fmaf(l, y[i], (1.f - l) * x[i]);
   }
   if (turns) {
     const int f0 = (c * 8) % half;
@@ -278,11 +294,12 @@ sink_attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T*
 
 // proj [T, ld]: q heads at q_off (nh x kd), k heads at k_off (nkv x kd), v heads at v_off (nkv x vd). wq, wk: float
 // [kd] or null (no norm). table: float [T, rot/2, 2] (cos, sin) or null (no rotation). slots [T] (-1: the
-// token's key and value are not stored) or null; kcache [pages, nkv, page, kd], vcache [pages, nkv, page, vd].
+// token's key and value are not stored) or null; kcache [pages, nkv, page, kd], vcache [pages, nkv, page, vd]. vfirst
+// (rows of proj's type with stride ldf: nkv heads of vd per token) with lam (one float on the device) or both null.
 RLLM_API int rllm_qk_norm_rope_store(int dt, void* proj, long long ld, int q_off, int k_off, int v_off, int n_tokens,
                                      int nh, int nkv, int kd, int vd, int rot, const float* wq, const float* wk,
                                      float eps, const float* table, const int* slots, void* kcache, void* vcache,
-                                     int page_size, void* stream) {
+                                     int page_size, const void* vfirst, long long ldf, const float* lam, void* stream) {
   if (n_tokens <= 0) return 0;
   if (kd <= 0 || kd > MAX_D || vd <= 0 || vd > MAX_D || nh <= 0 || nkv <= 0 || rot < 0 || rot > kd || rot % 2 ||
       page_size <= 0)
@@ -292,13 +309,15 @@ RLLM_API int rllm_qk_norm_rope_store(int dt, void* proj, long long ld, int q_off
   if (blocks > 2147483647LL) return ERR_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
   if (rot == 0) table = nullptr;
+  if ((vfirst != nullptr) != (lam != nullptr)) return ERR_BAD_SIZE;
   if (dt == DT_F32)
     return launch_ex(qk_norm_rope_store_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, s, 1, (float*)proj, ld, q_off,
                      k_off, v_off, n_tokens, nh, nkv, kd, vd, rot, wq, wk, eps, table, slots, (float*)kcache,
-                     (float*)vcache, page_size);
+                     (float*)vcache, page_size, (const float*)vfirst, ldf, lam);
   const bool vec = dt == DT_BF16 && kd % 8 == 0 && vd % 8 == 0 && rot % 16 == 0 && ld % 8 == 0 && q_off % 8 == 0 &&
                    k_off % 8 == 0 && v_off % 8 == 0 && !((uintptr_t)proj & 15) && !((uintptr_t)kcache & 15) &&
                    !((uintptr_t)vcache & 15) && !((uintptr_t)wq & 15) && !((uintptr_t)wk & 15) && !((uintptr_t)table & 15) &&
+                   !((uintptr_t)vfirst & 15) && ldf % 8 == 0 &&
                    (slots != nullptr) == (kcache != nullptr && vcache != nullptr);
   if (vec) {
     const int pieces = (kd > vd ? kd : vd) / 8;
@@ -309,7 +328,7 @@ RLLM_API int rllm_qk_norm_rope_store(int dt, void* proj, long long ld, int q_off
     if (vblocks > 2147483647LL) return ERR_TOO_LARGE;
 #define GO(L) return launch_ex(qk_norm_rope_store_vec_kernel<L>, dim3((unsigned)vblocks), dim3(128), 0, s, 1, (bf16*)proj, ld, \
                                q_off, k_off, v_off, n_tokens, nh, nkv, kd, vd, rot, wq, wk, eps, table, slots, (bf16*)kcache,  \
-                               (bf16*)vcache, page_size)
+                               (bf16*)vcache, page_size, (const bf16*)vfirst, ldf, lam)
     switch (lph) {
       case 1: GO(1);
       case 2: GO(2);
@@ -323,7 +342,7 @@ RLLM_API int rllm_qk_norm_rope_store(int dt, void* proj, long long ld, int q_off
   if (dt == DT_BF16)
     return launch_ex(qk_norm_rope_store_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, s, 1, (bf16*)proj, ld, q_off,
                      k_off, v_off, n_tokens, nh, nkv, kd, vd, rot, wq, wk, eps, table, slots, (bf16*)kcache,
-                     (bf16*)vcache, page_size);
+                     (bf16*)vcache, page_size, (const bf16*)vfirst, ldf, lam);
   return ERR_BAD_DTYPE;
 }
 

@@ -293,11 +293,13 @@ class Backend:
             return self._sink.relu2_(self._sm100.gemm(x, w, ops.EPI_STORE))
         return ops.gemm_simt(x, w, ops.EPI_RELU2)
 
-    def qk_norm_rope_store(self, proj, q_off, k_off, v_off, nh, nkv, kd, vd, rot, wq, wk, eps, table, cache):
+    def qk_norm_rope_store(self, proj, q_off, k_off, v_off, nh, nkv, kd, vd, rot, wq, wk, eps, table, cache, vfirst=None,
+                           lam=None):
+        """`vfirst`, `lam`: the values are cached as (1 - lam) v + lam vfirst (another layer's values of the same tokens)."""
         writes = cache.writes
         self._sink.qk_norm_rope_store(proj, q_off, k_off, v_off, nh, nkv, kd, vd, rot, wq, wk, eps, table,
                                       cache.slots if writes else None, cache.k if writes else None,
-                                      cache.v if writes else None)
+                                      cache.v if writes else None, vfirst if writes else None, lam if writes else None)
 
     def sink_attention(self, q, cache, ctx, nh, scale, window, chunk, sinks, gate, keep_first=0, sigmoid=False):
         """Attention with a window and/or block mask, a sink and an output gate over pages whose keys and values
@@ -434,10 +436,6 @@ class Backend:
         float tensors with a coefficient each)."""
         terms = list(y.terms) if hasattr(y, "terms") else [(y, 1.0)]
         return self._hy.gated_add(h, gate, bias, terms)
-
-    def mix_values(self, proj, v_off, n_cols, first, lam):
-        """The value columns of `proj` become (1 - lam) v + lam first, with `first` the rows another layer kept."""
-        return self._hy.lerp_cols(proj[:, v_off: v_off + n_cols], first, n_cols, lam)
 
     def mingru_scan(self, proj, z_off, x_off, g_off, width, bias_z, bias_x, ctx, state):
         return self._hy.mingru_scan(proj, z_off, x_off, g_off, width, bias_z, bias_x, ctx.cu_q, ctx.num_seqs,

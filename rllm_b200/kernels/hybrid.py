@@ -34,7 +34,6 @@ ops.register_signatures("hybrid", {
     "rllm_talk_attention_mma_supported": [c_int, c_int, c_int, c_int, c_int],
     "rllm_gated_add": [_P, _P, _LL, _P, _P, c_float, _P, c_float, c_int, c_int, _P],
     "rllm_act_rows": [_P, c_int, _LL, _P, c_int, c_int, c_int, c_int, _P],
-    "rllm_lerp_cols": [c_int, _P, _LL, _P, _LL, c_int, c_int, _P, _P],
     "rllm_mingru_scan": [_P, _LL, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P,
                          _P, _P],
     "rllm_talk_attention_mma": [_P, _LL, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -183,21 +182,6 @@ def gated_add(h, gate, bias, terms) -> torch.Tensor:
     _check(_fn("hybrid", "rllm_gated_add")(h.data_ptr(), gate.data_ptr(), gate.stride(0), _ptr(bias), y0.data_ptr(), float(c0),
                                            _ptr(y1), float(c1), T, W, _stream()), "gated_add")
     return h
-
-
-def lerp_cols(dst, src, n_cols, lam) -> torch.Tensor:
-    """dst[:, :n_cols] <- (1 - lam) dst[:, :n_cols] + lam src[:, :n_cols] in place, in float, rounded once. dst and src
-    rows of one type with unit inner stride (views with longer row strides are fine); `lam` one float32 on the device."""
-    _rows(dst, "dst", n_cols)
-    _rows(src, "src", n_cols)
-    if dst.dtype != src.dtype or dst.shape[0] != src.shape[0]:
-        raise KernelError("lerp_cols takes two sets of rows of one type and count")
-    _f32(lam, "lam")
-    if lam.numel() != 1:
-        raise KernelError("lerp_cols takes one coefficient")
-    _check(_fn("hybrid", "rllm_lerp_cols")(_dt(dst, "dst"), dst.data_ptr(), dst.stride(0), src.data_ptr(), src.stride(0),
-                                           dst.shape[0], int(n_cols), lam.data_ptr(), _stream()), "lerp_cols")
-    return dst
 
 
 # --------------------------------------------------------------------------- recurrent mixers

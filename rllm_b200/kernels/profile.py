@@ -291,10 +291,6 @@ class OpProfile:
         n = 3 + (len(y.terms) if hasattr(y, "terms") else 1)       # the stream read and written, the gate, the summands
         return self._timed("gate+add", n * _nbytes(h), 0, self._be.gated_add, h, gate, bias, y)
 
-    def mix_values(self, proj, v_off, n_cols, first, lam):
-        return self._timed("value_mix", 3 * proj.shape[0] * n_cols * proj.element_size(), 0, self._be.mix_values, proj, v_off,
-                           n_cols, first, lam)
-
     def mingru_scan(self, proj, z_off, x_off, g_off, width, bias_z, bias_x, ctx, state):
         T = proj.shape[0]
         pieces = 2 if ctx.max_q_len > 64 else 1                    # long portions read the gates' logits twice

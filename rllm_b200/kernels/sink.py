@@ -17,7 +17,7 @@ _P, _LL = ops._P, c_longlong
 
 ops.register_signatures("sink", {
     "rllm_qk_norm_rope_store": [c_int, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P,
-                                c_float, _P, _P, _P, _P, c_int, _P],
+                                c_float, _P, _P, _P, _P, c_int, _P, _LL, _P, _P],
     "rllm_sink_attention_simt": [c_int, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, c_int, _P],
     "rllm_sink_attention_mma_supported": [c_int, c_int, c_int, c_int],
@@ -55,11 +55,13 @@ def _caches(kcache, vcache, dtype, nkv=None):
 def qk_norm_rope_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nh: int, nkv: int, kd: int, vd: int,
                        rot: int, wq: torch.Tensor | None, wk: torch.Tensor | None, eps: float,
                        table: torch.Tensor | None, slots: torch.Tensor | None, kcache: torch.Tensor | None,
-                       vcache: torch.Tensor | None) -> None:
+                       vcache: torch.Tensor | None, vfirst: torch.Tensor | None = None, lam: torch.Tensor | None = None) -> None:
     """proj [T, cols] holds q (nh heads of kd at q_off), k (nkv of kd at k_off) and v (nkv of vd at v_off). Per
     head: q and k divided by their root mean square times `wq` / `wk` (float [kd]; None: no norm), then the
     first `rot` dimensions rotated (dimension i with i + rot/2) by `table` float [T, rot/2, 2] (cos, sin); q is
-    written back in place, k and v go to their pages at `slots` (None, or -1 for a token: not stored)."""
+    written back in place, k and v go to their pages at `slots` (None, or -1 for a token: not stored). `vfirst` (rows of
+    proj's type, [T, nkv * vd], a view with a longer row stride is fine) and `lam` (one float32 on the device): what is
+    stored as the value is (1 - lam) v + lam vfirst, formed in float and rounded once; proj keeps v as it was."""
     _cuda(proj, "proj")
     T = proj.shape[0]
     need = max(q_off + nh * kd, k_off + nkv * kd, v_off + nkv * vd)
@@ -79,10 +81,19 @@ def qk_norm_rope_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n
         if kcache.shape[3] != kd or vcache.shape[3] != vd:
             raise KernelError(f"pages hold keys of {kcache.shape[3]} and values of {vcache.shape[3]}, not {kd} and {vd}")
         page_size = kcache.shape[2]
+    if (vfirst is None) != (lam is None):
+        raise KernelError("values are mixed with rows and a coefficient, or not at all")
+    if vfirst is not None:
+        _cuda(vfirst, "vfirst")
+        _f32(lam, "lam")
+        if vfirst.dtype != proj.dtype or vfirst.dim() != 2 or vfirst.stride(1) != 1 or tuple(vfirst.shape) != (T, nkv * vd) \
+                or lam.numel() != 1:
+            raise KernelError(f"vfirst must be [{T}, {nkv * vd}] of {proj.dtype} with unit inner stride, lam one number")
     _check(_fn("sink", "rllm_qk_norm_rope_store")(
         _dt(proj, "proj"), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, T, nh, nkv, kd, vd, rot, _ptr(wq),
         _ptr(wk), float(eps), _ptr(table) if rot else None, _ptr(slots), _ptr(kcache) if slots is not None else None,
-        _ptr(vcache) if slots is not None else None, page_size, _stream()), "qk_norm_rope_store")
+        _ptr(vcache) if slots is not None else None, page_size, _ptr(vfirst), 0 if vfirst is None else vfirst.stride(0),
+        _ptr(lam), _stream()), "qk_norm_rope_store")
 
 
 def _attention_args(q, kcache, vcache, token_seq, positions, block_table, nh, sinks, gate):

@@ -162,17 +162,17 @@ class SinkGQAttention(Part):
         proj = be.linear(x, self.w_qkv, tag="qkv")                                  # [T, q | k | v]
         gate = be.linear_f32(x, self.w_g, tag="gate") if self.gate else None         # float logits [T, H]
         pos = self.position
+        first = lam = None
         if self.value_mix is not None:
             role, key = self.value_mix
             if role == "first":                  # this step's values, as projected, for the layers that mix them in
                 ctx.per_forward[("value_mix", key)] = proj[:, (H + G) * D:]
-            else:
-                first = ctx.per_forward.get(("value_mix", key))
+            else:                                # mixed on their way into the pages, by the kernel that writes them
+                first, lam = ctx.per_forward.get(("value_mix", key)), self._lam
                 if first is None or first.shape[1] != G * V:
                     raise ValueError(f"{self.prefix}: the values to mix in ({key!r}) are missing or of another size")
-                be.mix_values(proj, (H + G) * D, G * V, first, self._lam)
         be.qk_norm_rope_store(proj, 0, H * D, (H + G) * D, H, G, D, V, 0 if pos is None else pos.rot_dim,
-                              self._qn, self._kn, self.eps, None if pos is None else pos.table(ctx), cache)
+                              self._qn, self._kn, self.eps, None if pos is None else pos.table(ctx), cache, first, lam)
         att = be.sink_attention(proj[:, : H * D], cache, ctx, H, self.scale, self.window, self.chunk, self._sinks, gate,
                                 self.keep_first if self.window else 0, self.weights == "sigmoid")
         if residual is None:

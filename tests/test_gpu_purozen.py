@@ -104,20 +104,41 @@ def test_gated_sum_into_the_stream(W):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
-def test_gelu_rows_and_values_mixed_in_place(dtype):
+def test_gelu_rows(dtype):
     from rllm_b200.kernels import hybrid
     x = rnd(37, 50, seed=1, scale=2.5)
     got = hybrid.act_rows(x.to(DEV), DT[dtype], "gelu_tanh")
     assert got.dtype == DT[dtype] and rel(got, P.gelu_tanh(x.double())) < (2e-6 if dtype == "float32" else 5e-3)
-    # the value columns of wider rows, mixed with rows of another stride
-    a, b = rnd(23, 70, seed=2).to(DT[dtype]), rnd(23, 44, seed=3).to(DT[dtype])
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("nkv,vd", [(2, 24), (1, 12), (4, 64), (3, 40)])
+def test_values_mixed_on_their_way_into_the_pages(dtype, nkv, vd):
+    """The kernel that caches keys and values stores (1 - lam) v + lam v_first, formed in float and rounded once, and
+    leaves the projected rows as they were; rows without a slot are not stored."""
+    from rllm_b200.kernels import sink
+    T, nh, kd, page = 21, 2 * nkv, 16, 4
+    cols = (nh + nkv) * kd + nkv * vd
+    proj = rnd(T, cols + 8, seed=1).to(DT[dtype])
+    first = rnd(T, nkv * vd + 16, seed=2).to(DT[dtype])
     lam = torch.tensor([0.3125])
-    want = a.double().clone()
-    want[:, 30:60] = (1 - 0.3125) * a.double()[:, 30:60] + 0.3125 * b.double()[:, 10:40]
-    ad = a.to(DEV)
-    hybrid.lerp_cols(ad[:, 30:60], b.to(DEV)[:, 10:40], 30, lam.to(DEV))
-    assert rel(ad, want) < (2e-6 if dtype == "float32" else 5e-3)
-    assert torch.equal(ad[:, :30].cpu(), a[:, :30]) and torch.equal(ad[:, 60:].cpu(), a[:, 60:])
+    slots = torch.randperm(32)[:T].int()
+    slots[5] = -1
+    kc = torch.zeros(8, nkv, page, kd, dtype=DT[dtype], device=DEV)
+    vc = torch.zeros(8, nkv, page, vd, dtype=DT[dtype], device=DEV)
+    pd = proj.to(DEV)
+    sink.qk_norm_rope_store(pd[:, :cols], 0, nh * kd, (nh + nkv) * kd, nh, nkv, kd, vd, 0, None, None, 1e-6, None, slots.to(DEV), kc, vc,
+                            first.to(DEV)[:, 8: 8 + nkv * vd], lam.to(DEV))
+    assert torch.equal(pd.cpu(), proj)
+    v = proj[:, (nh + nkv) * kd: cols].double().view(T, nkv, vd)
+    want = (1 - 0.3125) * v + 0.3125 * first[:, 8: 8 + nkv * vd].double().view(T, nkv, vd)
+    for t in range(T):
+        s_ = int(slots[t])
+        if s_ < 0:
+            continue
+        assert rel(vc[s_ // page, :, s_ % page], want[t]) < (2e-6 if dtype == "float32" else 5e-3)
+        assert torch.equal(kc[s_ // page, :, s_ % page].cpu(), proj[t, nh * kd: (nh + nkv) * kd].view(nkv, kd))
+    assert int((vc.abs().sum((1, 3)) > 0).sum()) == T - 1
 
 
 @pytest.mark.parametrize("dtype", list(DT))
