@@ -28,7 +28,10 @@
 // after are computed already, and a row tile that has written its P goes on at once: the four warp
 // schedulers always have a warp with work (two warps each, one of either tile).
 // TMEM: three S accumulators and PV of both tiles, 512 columns.
-// A key j is visible when j <= position of the row and j > position - window.
+// A key j is visible when j <= position of the row and j > position - window, or when j <= position and j <
+// keep_first (kept first keys): the tiles of the kept keys that the window's walk does not reach are walked first, then
+// the window's, as one list. With `sigmoid` a visible key's weight is sigmoid(score + bias[head]) in place of the
+// softmax's: no maximum, no rescaling, no denominator.
 //
 // Formulas: src/gpu/cuda/shaders/attention.cu:573-618 and :328-388 of the reference (scale,
 // softmax with the maximum subtracted, weighted V, head h -> kv head h / G, window); unlike the
@@ -88,7 +91,10 @@ struct PfParams {
   const int* cu_q; const int* kv_lens; const int* block_table; int bt_stride;
   int nh, nkv, page_size, page_shift, window;
   int chunk;             // > 0: a row sees only the keys of its own block of this many positions
-  const float* sinks;    // per head, or null: exp(sink) joins a row's denominator (no key, no value)
+  const float* sinks;    // per head, or null: exp(sink) joins a row's denominator (no key, no value); with
+                         // `sigmoid` the heads' biases instead
+  int keep_first;        // positions below this number are seen whatever the window says
+  int sigmoid;           // != 0: weights sigmoid(score + bias), not normalised
   const float* gate;     // float logits [T, gate_ld] or null: head h's output times sigmoid(gate[t, h])
   int gate_ld;
   int box_rows;          // TMA variant: keys per copy = min(page size, 128)
@@ -97,6 +103,11 @@ struct PfParams {
   int* err;
 };
 
+__device__ __forceinline__ float fast_rcp(float x) {           // 1 / inf = 0; relative error about 2^-23
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float fast_exp2(float x) {          // exp2(-inf) = 0
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -190,19 +201,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   const int rows_total = q_len * G;
   // keys the item's rows can see at all: from the first row's window (or 0) to the last row's position.
   // The later row tile sees at least as far as the earlier one; both start from the same tile.
-  int kv_begin = 0, n_t[RT];
+  // With kept first keys the tiles [0, n_kept) of those keys come first in the list (only the ones that lie wholly
+  // before the window's first tile; a kept key inside the window's tiles is seen there).
+  int kv_begin = 0, n_kept = 0, n_t[RT];
   {
     const int p_min = kv_len - q_len + (tile0 * PM) / G;
     int first = (p.window > 0 && p_min - p.window + 1 > 0) ? p_min - p.window + 1 : 0;
     if (p.chunk > 0) first = max(first, p_min / p.chunk * p.chunk);
     kv_begin = first / PN * PN;
+    n_kept = min((min(p.keep_first, first) + PN - 1) / PN, kv_begin / PN);
 #pragma unroll
     for (int g = 0; g < RT; ++g) {
       const bool active = (tile0 + g) * PM < rows_total;         // uniform: a row tile beyond the sequence's rows is empty
       const int p_max = kv_len - q_len + min(q_len - 1, ((tile0 + g) * PM + PM - 1) / G);
-      n_t[g] = active ? (p_max + 1 - kv_begin + PN - 1) / PN : 0;
+      n_t[g] = active ? n_kept + (p_max + 1 - kv_begin + PN - 1) / PN : 0;
     }
   }
+  auto tile_first = [&](int t) { return t < n_kept ? t * PN : kv_begin + (t - n_kept) * PN; };   // first key of tile t of the list
   const int n_tiles = max(n_t[0], n_t[1]);
   // step k is (row tile, K tile) = (k & 1, k >> 1) while both row tiles have tiles left, then the later one alone
   const int n_both = min(n_t[0], n_t[1]), g_long = n_t[1] > n_t[0] ? 1 : 0, n_steps = n_t[0] + n_t[1];
@@ -295,7 +310,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           }
           if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
         }
-        const int j = kv_begin + t * PN + cp * p.box_rows;              // first key of this lane's copy
+        const int j = tile_first(t) + cp * p.box_rows;                  // first key of this lane's copy
         const bool mine = cp < copies && j < kv_len;
         const int page = mine ? __ldg(bt + (j >> p.page_shift)) : 0;
         const uint32_t n = __popc(__ballot_sync(0xffffffffu, mine));
@@ -335,7 +350,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         if (__shfl_sync(0xffffffffu, w_ok, 0) == 0) break;
       }
       if (t == 0) load_q(0, RT * PM);                     // lands with the tile, announced by its barrier
-      const int j0 = kv_begin + t * PN;
+      const int j0 = tile_first(t);
       const uint32_t kd = k_s + (uint32_t)s * KV_TILE_BYTES, vd = v_s + (uint32_t)s * KV_TILE_BYTES;
 #pragma unroll 1
       for (int i0 = 0; i0 < PN / 4; i0 += 8) {
@@ -421,8 +436,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const float sl = p.scale_log2e;
     // m: what the exponentials are taken against, up to 2^8 behind the true maximum. A sink opens the row's
     // running softmax as a key of score `sink` (not scaled) and value zero.
-    const bool sunk = p.sinks != nullptr && valid;
+    const bool sig = p.sigmoid != 0;
+    const bool sunk = !sig && p.sinks != nullptr && valid;
     float m = sunk ? p.sinks[head] * 1.4426950408889634f : -INFINITY, l = sunk ? 1.f : 0.f;
+    const float sb = (sig && p.sinks != nullptr && valid) ? p.sinks[head] * 1.4426950408889634f : 0.f;   // the bias, log2 domain
+    const int kf = p.keep_first;
     bool ok = true;
 
     auto wait_on = [&](uint64_t* bar, uint32_t parity, int role, int t) -> bool {
@@ -432,7 +450,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     };
 
     for (int t = 0; t < n_mine; ++t) {
-      const int j0 = kv_begin + t * PN;
+      const int j0 = tile_first(t);
       const int k = t < n_both ? 2 * t + g : 2 * n_both + (t - n_both);
       const uint32_t s_addr = lane_addr + C::S_COL + (uint32_t)(k % SB) * PN;   // this step's S accumulator
       if (!wait_on(&s_full[k % SB], (uint32_t)(k / SB) & 1u, 24, t)) { ok = false; break; }
@@ -445,13 +463,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[k % SB]);        // the accumulator may take the scores of step k + 3
-      if (!valid || j0 + PN - 1 > pos || j0 < lo) {        // some key is hidden from this row
+      if (!valid || j0 + PN - 1 > pos || (j0 < lo && j0 + PN > kf)) {        // some key is hidden from this row
 #pragma unroll
         for (int c = 0; c < NC; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int j = j0 + 32 * c + i;
-            if (!(valid && j <= pos && j >= lo)) v[c][i] = 0xff800000u;
+            if (!(valid && j <= pos && (j >= lo || j < kf))) v[c][i] = 0xff800000u;
           }
       }
       float mq[NC];                                       // chains side by side, not one of 64 links
@@ -465,7 +483,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
 #pragma unroll
       for (int c = 1; c < NC; ++c) mx = fmaxf(mx, mq[c]);
       const float cand = fmaxf(m, mx * sl);               // the scale is positive: it commutes with max
-      const bool move = cand > m + 8.f;                   // also the first visible key (m = -inf)
+      const bool move = !sig && cand > m + 8.f;           // also the first visible key (m = -inf)
       float corr = 1.f;
       if (move) { corr = fast_exp2(m - cand); m = cand; l *= corr; }      // exp2(-inf) = 0
       if (t > 0) {
@@ -496,10 +514,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
 #pragma unroll
         for (int q8 = 0; q8 < 4; ++q8) {                  // 8 keys = one 16-byte chunk
           float e[8];
+          if (sig) {
+            // sigmoid(x) = 1 / (1 + 2^(-x log2 e)); hidden keys hold -inf: 1 / (1 + inf) = 0
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            e[i] = fast_exp2(fmaf(__uint_as_float(v[c][8 * q8 + i]), sl, -use));      // hidden keys hold -inf: 0
-            lq[i] += e[i];
+            for (int i = 0; i < 8; ++i) e[i] = fast_rcp(1.f + fast_exp2(-fmaf(__uint_as_float(v[c][8 * q8 + i]), sl, sb)));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              e[i] = fast_exp2(fmaf(__uint_as_float(v[c][8 * q8 + i]), sl, -use));      // hidden keys hold -inf: 0
+              lq[i] += e[i];
+            }
           }
           const int ch = (c & 1) * 4 + q8;
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + (uint32_t)((ch ^ (r & 7)) << 4)),
@@ -515,7 +539,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     }
     if (ok && wait_on(&pv_full[g], (uint32_t)(n_mine - 1) & 1u, 25, n_mine)) {
       tc_fence_after();
-      float inv = l > 0.f ? 1.f / l : 0.f;
+      float inv = sig ? 1.f : (l > 0.f ? 1.f / l : 0.f);
       if (p.gate && valid) inv *= 1.f / (1.f + __expf(-p.gate[(size_t)(q0 + tok) * p.gate_ld + head]));
       bf16* dst = p.out + (size_t)(q0 + tok) * p.out_stride + (size_t)head * HD;
 #pragma unroll
@@ -617,16 +641,17 @@ int launch_pf(const CUtensorMap& mk, const CUtensorMap& mv, const PfParams& p, i
 // kcache / vcache: [num_pages][nkv][page_size][hd] bf16. cu_q [S+1], kv_lens [S], block_table [S, bt_stride].
 // max_q_len: the longest portion in the batch (sizes the list of work items). Head sizes 64 and 128.
 // chunk > 0: a query sees only the keys of its own block of `chunk` positions (blocks counted from position 0);
-// sinks: float [nh] or null; gate: float logits [T, gate_ld] or null (see PfParams).
+// sinks: float [nh] or null; gate: float logits [T, gate_ld] or null (see PfParams); keep_first, sigmoid: see PfParams.
 // sm_count: CTAs to launch at most (0: asked from the device).
 RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* kcache, const void* vcache,
                                        void* out, int out_stride, const int* cu_q, const int* kv_lens,
                                        const int* block_table, int bt_stride, int num_seqs, int max_q_len,
                                        int num_pages, int nh, int nkv, int hd, int page_size, float scale, int window,
                                        int chunk, const float* sinks, const float* gate, int gate_ld,
-                                       int* err, int sm_count, void* stream) {
+                                       int keep_first, int sigmoid, int* err, int sm_count, void* stream) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
-  if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0) return ERR_BAD_SIZE;
+  if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0 || keep_first < 0 || scale <= 0.f)
+    return ERR_BAD_SIZE;
   if (q_stride % 8 || out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
       ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15)) return ERR_BAD_ALIGN;
   PfParams p;
@@ -635,7 +660,7 @@ RLLM_API int rllm_attention_prefill_tc(const void* q, int q_stride, const void* 
   p.block_table = block_table; p.bt_stride = bt_stride; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
   p.page_shift = -1;
   if ((page_size & (page_size - 1)) == 0) { p.page_shift = 0; while ((1 << p.page_shift) < page_size) ++p.page_shift; }
-  p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_ld = gate_ld;
+  p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_ld = gate_ld; p.keep_first = keep_first; p.sigmoid = sigmoid;
   p.window = window; p.scale_log2e = scale * 1.4426950408889634f; p.err = err;
   const int G = nh / nkv;
   p.row_pairs = (max_q_len * G + RT * PM - 1) / (RT * PM); p.num_seqs = num_seqs;

@@ -316,18 +316,20 @@ class Backend:
         if chunk:
             keys = min(keys, chunk)
         G = nh // nkv
-        if tc and kd == vd and not keep_first and not sigmoid and self._sm100.attention_supported(q, cache.k):
+        if tc and kd == vd and self._sm100.attention_supported(q, cache.k):
             # equal head sizes of 64 or 128: the kernels of plain grouped-query attention take the mask, the sink
-            # and the gate as well (the clusters of the decode kernel, tcgen05 for long portions)
+            # and the gate as well (the clusters of the decode kernel, tcgen05 for long portions); kept first keys and
+            # sigmoid weights only the tcgen05 kernel does
             sm = self._sm100
-            if ctx.max_q_len == 1 and sm.decode_supported(q, cache.k, nh):
+            if ctx.max_q_len == 1 and not keep_first and not sigmoid and sm.decode_supported(q, cache.k, nh):
                 return sm.attention_decode(q, cache.k, cache.v, ctx.kv_lens, cache.block_table, nh, scale, window, keys,
                                            chunk=chunk, sinks=sinks, gate=gate)
             lens = ctx.q_lens_host
             if ctx.max_q_len * G >= 128 and ctx.max_kv_len >= sm.TC_ATTENTION_MIN_KEYS and sm.prefill_tc_supported(q, cache.k) \
                     and lens is not None and min(lens) * G >= 128:
                 return sm.attention_prefill_tc(q, cache.k, cache.v, ctx.cu_q, ctx.kv_lens, cache.block_table, ctx.max_q_len,
-                                               nh, scale, window, chunk=chunk, sinks=sinks, gate=gate)
+                                               nh, scale, window, chunk=chunk, sinks=sinks, gate=gate, keep_first=keep_first,
+                                               sigmoid=sigmoid)
         if tc and sk.mma_supported(q.dtype, kd, vd, cache.page_size):
             tiles = 0
             for ql in (ctx.q_lens_host if not ctx.graph_safe else [1] * ctx.num_seqs):

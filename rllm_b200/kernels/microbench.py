@@ -416,6 +416,12 @@ def cmd_gated(a) -> None:
         q = bf(T, nh * kd)
         pos, seq = torch.arange(T, device=DEV, dtype=torch.int32), torch.zeros(T, device=DEV, dtype=torch.int32)
         pairs = T * (T + 1) / 2
+        if a.plain and a.tcgen05:
+            lens, out = i32([T]), torch.empty(T, nh * vd, device=DEV, dtype=torch.bfloat16)
+            run([lambda: sm100.attention_prefill_tc(q, kc, vc, cu, lens, bt, T, nh, scale, None, out=out, sinks=bias, sigmoid=True)],
+                a.plain, f"sigmoid attention (tcgen05) T={T} heads of {kd}")
+            sm100.check_error(DEV)
+            return
         run([lambda: sink.sink_attention_mma(q, kc, vc, seq, pos, bt, cu, 1, T, nh, scale, None, None, bias, None, 1, T, 0, True)] * 4,
             a.plain, f"sigmoid attention (mma.sync) T={T} heads={nh}/{nkv} of {kd}/{vd}", flops=2.0 * nh * (kd + vd) * pairs)
         if a.plain:
@@ -428,6 +434,16 @@ def cmd_gated(a) -> None:
             f"windowed attention with kept first keys T={T} window={win} kept={kept}", flops=2.0 * nh * (kd + vd) * wpairs)
         run([lambda: sink.sink_attention_mma(q, kc, vc, seq, pos, bt, cu, 1, T, nh, scale, win, None, None, None, 1, T)] * 4, 0,
             f"  like: the window alone T={T}", flops=2.0 * nh * (kd + vd) * sum(min(i + 1, win) for i in range(T)))
+        if kd == vd and kd in (64, 128):                 # equal head sizes: long portions take the tcgen05 kernel
+            lens, out = i32([T]), torch.empty(T, nh * vd, device=DEV, dtype=torch.bfloat16)
+            run([lambda: sm100.attention_prefill_tc(q, kc, vc, cu, lens, bt, T, nh, scale, None, out=out, sinks=bias, sigmoid=True)] * 4, 0,
+                f"sigmoid attention (tcgen05) T={T} heads of {kd}", flops=4.0 * nh * kd * pairs)
+            run([lambda: sm100.attention_prefill_tc(q, kc, vc, cu, lens, bt, T, nh, scale, None, out=out)] * 4, 0,
+                f"  like: softmax attention (tcgen05) T={T}", flops=4.0 * nh * kd * pairs)
+            run([lambda: sm100.attention_prefill_tc(q, kc, vc, cu, lens, bt, T, nh, scale, win, out=out, keep_first=kept)] * 4, 0,
+                f"windowed attention with kept first keys (tcgen05) T={T} window={win} kept={kept}", flops=4.0 * nh * kd * wpairs)
+            run([lambda: sm100.attention_prefill_tc(q, kc, vc, cu, lens, bt, T, nh, scale, win, out=out)] * 4, 0,
+                f"  like: the window alone (tcgen05) T={T}", flops=4.0 * nh * kd * sum(min(i + 1, win) for i in range(T)))
         # the gated recurrence beside the state scan over as many channels (heads of 128 x 64 hold 64 times the state)
         R = a.channels or W
         proj, bz, bx = torch.randn(T, 3 * R, device=DEV), torch.randn(R, device=DEV), torch.randn(R, device=DEV)
@@ -519,6 +535,7 @@ def main(argv=None) -> int:
         p.add_argument("--" + k, type=int, default=v)
     p = sub.add_parser("gated")
     p.add_argument("--plain", type=int, default=0, help="N plain launches of the sigmoid attention kernel instead of timing")
+    p.add_argument("--tcgen05", action="store_true", help="with --plain: the tcgen05 kernel (equal head sizes of 64 or 128)")
     p.add_argument("--tokens", type=ints, default=[2048])
     p.add_argument("--batch", type=ints, default=[8, 64])
     for k, v in (("heads", 16), ("kv-heads", 4), ("dim", 128), ("vdim", 128), ("page", 16), ("context", 1024), ("window", 1024),

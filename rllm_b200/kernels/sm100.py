@@ -29,7 +29,7 @@ ops.register_signatures("sm100", {
     "rllm_attention_fa": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_int, _P, _P, _P],
     "rllm_attention_prefill_tc": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_int, c_float, c_int, c_int, _P, _P, c_int, _P, c_int, _P],
+                                  c_int, c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, c_int, _P, c_int, _P],
     "rllm_attention_decode": [_P, c_int, _P, _P, c_longlong, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, _P, _P],
 })
@@ -348,11 +348,12 @@ def _extras(chunk, sinks, gate, nh, rows):
 
 
 def attention_prefill_tc(q, kcache, vcache, cu_q, kv_lens, block_table, max_q_len, nh, scale, window, out=None,
-                         chunk=None, sinks=None, gate=None):
+                         chunk=None, sinks=None, gate=None, keep_first=0, sigmoid=False):
     """Prefill attention on the tcgen05 tensor cores (bf16, head size 64 or 128): tiles of 128 rows x
     128 (64) keys, both products with their accumulators in TMEM. `chunk`: a query sees only the keys of its
     own block of that many positions; `sinks` float [nh]: exp(sink) joins a row's denominator; `gate` float
-    logits [T, >= nh]: head h's output times sigmoid(gate[t, h])."""
+    logits [T, >= nh]: head h's output times sigmoid(gate[t, h]); `keep_first`: positions below it are seen whatever
+    the window says; `sigmoid`: no softmax, a visible key's weight is sigmoid(score + sinks[head])."""
     if not prefill_tc_supported(q, kcache):
         raise ops.KernelError("attention_prefill_tc: bfloat16, head size 64 or 128, rows 16-byte aligned")
     st = init(q.device)
@@ -363,7 +364,8 @@ def attention_prefill_tc(q, kcache, vcache, cu_q, kv_lens, block_table, max_q_le
         q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(), out.stride(0),
         cu_q.data_ptr(), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), kv_lens.numel(),
         max_q_len, kcache.shape[0], nh, nkv, hd, page_size, float(scale), int(window or 0),
-        *_extras(chunk, sinks, gate, nh, q.shape[0]), st.err.data_ptr(), st.sm_count, ops._stream())
+        *_extras(chunk, sinks, gate, nh, q.shape[0]), int(keep_first or 0), int(bool(sigmoid)), st.err.data_ptr(),
+        st.sm_count, ops._stream())
     ops._check(rc, "attention_prefill_tc")
     return out
 

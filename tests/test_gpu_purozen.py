@@ -504,6 +504,89 @@ def test_far_kept_and_edge_keys_in_long_contexts_on_both_kernels(window, kept, s
                 assert rel(got1, want[one]) < tol, splits
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("window,kept,sigmoid", [(None, 0, True), (300, 70, False), (128, 128, False), (100, 3, False), (257, 200, True),
+                                                  (64, 1, False)])
+def test_long_portions_with_equal_head_sizes_on_tcgen05(hd, window, kept, sigmoid):
+    """Equal key and value sizes of 64 or 128: long portions take the tcgen05 kernel, which walks the kept keys' tiles
+    before the window's and has the sigmoid branch. Three portions beside each other (one with all its keys in the step,
+    one behind 800 cached keys, one short), a kept key, the last kept key and the first that is not, and keys just
+    inside and just outside the last query's window made to stand out; against the float kernel on the same cache."""
+    from rllm_b200.kernels import sink, sm100
+    g = torch.Generator().manual_seed(hd + (window or 0))
+    nh, nkv, page, n_pages = 8, 2, 16, 100
+    lens, qlens = [1500, 700, 1024], [700, 700, 130]
+    S = len(lens)
+    kc = (torch.randn(n_pages * S, nkv, page, hd, generator=g) * 0.5).bfloat16().to(DEV)
+    vc = torch.randn(n_pages * S, nkv, page, hd, generator=g).bfloat16().to(DEV)
+    bt = torch.randperm(n_pages * S, generator=g).int().view(S, n_pages).contiguous().to(DEV)
+    bias = (torch.randn(nh, generator=g) * 2 - 3).to(DEV) if sigmoid else None
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    T = sum(qlens)
+    q = torch.randn(T, nh * hd, generator=g).bfloat16().to(DEV)
+    last = q[qlens[0] - 1].view(nh, hd)[::4]                   # the last query of the first portion, one head per kv head
+    marks = [0, 99] if window is None else [0, max(kept - 1, 0), kept, 1499 - window + 1, 1499 - window]
+    for far in marks:
+        kc[bt[0, far // page].item(), :, far % page] = last * 2
+    cu = torch.tensor([0, 700, 1400, 1530], dtype=torch.int32, device=DEV)
+    pos = torch.cat([torch.arange(n - ql, n) for n, ql in zip(lens, qlens)]).int().to(DEV)
+    seq = torch.cat([torch.full((ql,), i) for i, ql in enumerate(qlens)]).int().to(DEV)
+    want = sink.sink_attention_simt(q, kc, vc, seq, pos, bt, nh, 0.11, window, None, bias, None, kept, sigmoid)
+    got = sm100.attention_prefill_tc(q, kc, vc, cu, kv, bt, max(qlens), nh, 0.11, window, sinks=bias, keep_first=kept, sigmoid=sigmoid)
+    sm100.check_error(DEV)
+    assert rel(got, want) < 2e-2
+    got = sink.sink_attention_mma(q, kc, vc, seq, pos, bt, cu, S, max(qlens), nh, 0.11, window, None, bias, None, 1, 1500, kept, sigmoid)
+    assert rel(got, want) < 2e-2
+    # the float kernel itself against plain arithmetic, for the marked query
+    i, r = 1499, qlens[0] - 1
+    j = torch.arange(i + 1)
+    seen = torch.ones(i + 1, dtype=torch.bool) if window is None else ((i - j < window) | (j < kept))
+    pages = bt[0].cpu()[j // page].long()
+    K = kc.cpu()[pages, :, j % page].double().repeat_interleave(nh // nkv, 1)          # [keys, heads, hd]
+    V = vc.cpu()[pages, :, j % page].double().repeat_interleave(nh // nkv, 1)
+    sc = torch.einsum("hd,jhd->hj", q[r].cpu().double().view(nh, hd), K) * 0.11
+    w_ = torch.sigmoid(sc + bias.cpu().double()[:, None]) * seen if sigmoid else torch.softmax(sc.masked_fill(~seen, float("-inf")), 1)
+    assert rel(want[r].cpu().double().view(nh, hd), torch.einsum("hj,jhd->hd", w_, V)) < 2e-2
+
+
+def test_the_engine_sends_long_portions_of_equal_head_sizes_to_tcgen05():
+    """A windowed attention layer with kept first tokens and a sigmoid attention layer, heads of 64 / 64: a portion of
+    600 tokens behind 200 cached ones runs on the tcgen05 kernel, single tokens on the `mma.sync` kernel; both agree
+    with the plain implementation."""
+    from rllm_b200.kernels import sink, sm100
+    W, n, eps, dtype = 64, 860, 1e-5, "bfloat16"
+    m = winm(4, 2, 64, 64, 0.125, (150, 70), (20000.0, 32, 2.0))
+    w = {**win_weights(W, m, 5, "a."), **win_weights(W, m, 9, "b.")}
+    h1, h2 = rnd(n, W, seed=9), rnd(n, W, seed=19)
+    for p in (0, 69, 70, 799 - 150, 799 - 149, 799, 859 - 150, 859 - 149, 859):
+        h1[p, 0] += 8.0
+        h2[p, 0] += 8.0
+    x1, x2 = h1.to(DT[dtype]), h2.to(DT[dtype])
+    st, sa = as_stored(w, dtype, prefix=""), stored_as(dtype)
+    want1, own = P.window_attention(x1.double(), st, "a.", m, eps, stored=sa)
+    want2, _ = P.window_attention(x2.double(), st, "b.", m, eps, v_first=own, stored=sa)
+    first, second = make_win(W, m, eps, "first"), make_win(W, m, eps, "mix")
+    bind(first, w, dtype, "a.")
+    bind(second, w, dtype, "b.")
+    calls = {"tc": 0, "mma": 0}
+    real_tc, real_mma = sm100.attention_prefill_tc, sink.sink_attention_mma
+    sm100.attention_prefill_tc = lambda *a, **k: (calls.__setitem__("tc", calls["tc"] + 1), real_tc(*a, **k))[1]
+    sink.sink_attention_mma = lambda *a, **k: (calls.__setitem__("mma", calls["mma"] + 1), real_mma(*a, **k))[1]
+    try:
+        hs = TwoLayers(dtype, [first.cache_spec()] * 2, page_size=16, pages=60)
+        d1, d2 = x1.to(DEV), x2.to(DEV)
+        got, i = [], 0
+        for qn in [200, 600] + [1] * 60:
+            got.append(hs.run([("a", qn)], lambda ctx, caches: torch.cat(
+                [first.forward(d1[i: i + qn], ctx, caches[0]), second.forward(d2[i: i + qn], ctx, caches[1])], 1)))
+            i += qn
+        sm100.check_error(DEV)
+    finally:
+        sm100.attention_prefill_tc, sink.sink_attention_mma = real_tc, real_mma
+    assert calls["tc"] == 2 and calls["mma"] == 2 * 61          # the portion of 200 has fewer keys than the tcgen05 kernel asks for
+    assert rel(torch.cat(got), torch.cat([want1, want2], 1)) < 2e-2
+
+
 # ------------------------------------------------------------------ attention over latents without positions, over steps
 
 def lat_weights(W, m, seed):
